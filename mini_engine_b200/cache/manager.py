@@ -32,6 +32,7 @@ class GroupSpec:
     num_kv_heads: int
     head_dim: int
     cache_slots: tuple[int, ...]     # the model's cache slots that live in this group
+    planes: int = 2                  # 2: keys and values; 1: one row per token and head
 
 
 class CacheHolder:

@@ -31,10 +31,13 @@ def read_config_json(folder: str) -> dict[str, Any]:
 
 
 def architecture_name(raw: dict[str, Any]) -> str:
+    """``"architectures": [name]`` (the first entry), or ``"architecture": name``."""
     archs = raw.get("architectures")
-    if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures': [name] entry")
-    return archs[0]
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
+    raise ConfigError("config.json has neither an 'architectures': [name] nor an 'architecture': name entry")
 
 
 def _need(raw: dict, key: str, kind):
@@ -180,3 +183,84 @@ class Qwen3Config(ModelConfig):
         if not self.use_sliding_window:
             d.pop("layer_types")
         return d
+
+
+_LOGOZEN_MIXERS = {
+    "latent_attention": {"heads": int, "dim": int, "rot_dim": int, "vdim": int, "kv_rank": int, "scale": float},
+    "mlstm": {"heads": int, "dim": int, "vdim": int, "gate_cap": float},
+}
+
+
+@dataclass
+class LogozenConfig(ModelConfig):
+    """Logozen: a decoder whose layers each name their mixer (attention through a latent, or an mLSTM recurrence) and an
+    optional dense PolyNorm feed-forward, over several residual streams with a short convolution in front of every
+    sub-layer.  config.json keys: ``vocab``, ``width``, ``streams``, ``embedding.scale``, ``norm.eps``, ``canon.taps``
+    and ``layers``: a list of ``{"type", "mixer": {sizes and constants}, "mlp": {"kind": "dense", "ff"} | null}``.
+    The design has no limit on positions; ``max_position_embeddings`` is what an int32 position allows the engine."""
+
+    streams: int = 1
+    embedding_scale: float = 1.0
+    norm_eps: float = 0.0
+    canon_taps: int = 1
+    layers: list[dict[str, Any]] = field(default_factory=list)
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "LogozenConfig":
+        def sub(key):
+            v = raw.get(key)
+            if not isinstance(v, dict):
+                raise ConfigError(f"config.json lacks the object {key!r}")
+            return v
+        layers = _need(raw, "layers", list)
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("config.json key 'layers' must be a list with at least one layer")
+        checked = []
+        for i, layer in enumerate(layers):
+            if not isinstance(layer, dict) or layer.get("type") not in _LOGOZEN_MIXERS:
+                raise ConfigError(f"layer {i}: 'type' must be one of {sorted(_LOGOZEN_MIXERS)}, got "
+                                  f"{layer.get('type') if isinstance(layer, dict) else layer!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"layer {i}: lacks the object 'mixer'")
+            m = {k: _need(mixer, k, kind) for k, kind in _LOGOZEN_MIXERS[layer["type"]].items()}
+            if layer["type"] == "latent_attention":
+                rot = mixer.get("rot")
+                if not isinstance(rot, dict):
+                    raise ConfigError(f"layer {i}: a latent_attention mixer lacks the object 'rot'")
+                m["rot"] = {"base": _need(rot, "base", float), "dims": _need(rot, "dims", int)}
+                if m["rot"]["dims"] % 2 or not 0 <= m["rot"]["dims"] <= m["rot_dim"]:
+                    raise ConfigError(f"layer {i}: rot.dims {m['rot']['dims']} must be even and at most rot_dim {m['rot_dim']}")
+                if not m["rot"]["base"] > 0:
+                    raise ConfigError(f"layer {i}: rot.base must be positive")
+            elif not m["gate_cap"] > 0:
+                raise ConfigError(f"layer {i}: gate_cap must be positive")
+            if any(v < 1 for k, v in m.items() if isinstance(v, int) and k != "rot_dim") or m.get("rot_dim", 0) < 0:
+                raise ConfigError(f"layer {i}: the mixer's sizes must be positive: {m}")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+                    raise ConfigError(f"layer {i}: 'mlp' must be null or of kind 'dense', got {mlp!r}")
+                mlp = {"kind": "dense", "ff": _need(mlp, "ff", int)}
+                if mlp["ff"] < 1:
+                    raise ConfigError(f"layer {i}: mlp.ff must be positive")
+            checked.append({"type": layer["type"], "mixer": m, "mlp": mlp})
+        eos = raw.get("eos_token_id", -1)
+        cfg = cls(architecture=architecture_name(raw), vocab_size=_need(raw, "vocab", int), hidden_size=_need(raw, "width", int),
+                  num_hidden_layers=len(checked), max_position_embeddings=int(raw.get("max_position_embeddings", 1 << 30)),
+                  eos_token_id=-1 if eos is None else int(eos), streams=int(raw.get("streams", 1)),
+                  embedding_scale=_need(sub("embedding"), "scale", float), norm_eps=_need(sub("norm"), "eps", float),
+                  canon_taps=_need(sub("canon"), "taps", int), layers=checked)
+        for name in ("vocab_size", "hidden_size", "streams", "canon_taps"):
+            if getattr(cfg, name) < 1:
+                raise ConfigError(f"{name} must be positive, got {getattr(cfg, name)}")
+        if cfg.streams > 8:
+            raise ConfigError(f"{cfg.streams} residual streams are not supported (up to 8)")
+        if not cfg.norm_eps > 0:
+            raise ConfigError("norm.eps must be positive")
+        return cfg
+
+    def to_json_dict(self) -> dict[str, Any]:
+        return {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "streams": self.streams,
+                "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps}, "canon": {"taps": self.canon_taps},
+                "layers": self.layers}

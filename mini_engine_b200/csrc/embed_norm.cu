@@ -7,10 +7,13 @@
 
 // A negative id ~j stands for ``feedback[j]``: the token that the step before drew for row j, still on the
 // device.  That lets the host launch a decode step before it has read the step before it.
+// The row is multiplied by ``scale`` and written ``copies`` times, ``copy_stride`` elements apart (a model that
+// keeps several residual streams starts them all from the embedding).
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, int* __restrict__ err,
-                             const int* __restrict__ feedback, int n_feedback) {
+                             const int* __restrict__ feedback, int n_feedback, float scale, int copies,
+                             int64_t copy_stride) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -20,17 +23,21 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
   if (!ok && threadIdx.x == 0) atomicOr(err, 1);
   const TW* row = table + (int64_t)(ok ? id : 0) * H;
   float* o = out + (int64_t)t * H;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) o[h] = ok ? to_f<TW>(row[h]) : 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float v = ok ? to_f<TW>(row[h]) * scale : 0.f;
+    for (int c = 0; c < copies; ++c) o[c * copy_stride + h] = v;
+  }
 }
 
 ME_API int me_embed(const int* ids, const void* table, int table_dtype, float* out, int T, int H,
-                    int V, int* err, const int* feedback, int n_feedback, cudaStream_t stream) {
+                    int V, int* err, const int* feedback, int n_feedback, float scale, int copies,
+                    int64_t copy_stride, cudaStream_t stream) {
   if (T == 0) return 0;
-  ME_REQUIRE(T > 0 && H > 0 && V > 0, "me_embed: bad sizes T=%d H=%d V=%d", T, H, V);
+  ME_REQUIRE(T > 0 && H > 0 && V > 0 && copies >= 1, "me_embed: bad sizes T=%d H=%d V=%d copies=%d", T, H, V, copies);
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   ME_DISPATCH_DTYPE(table_dtype, TW,
                     me_launch(embed_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, err,
-                              feedback, n_feedback));
+                              feedback, n_feedback, scale, copies, copy_stride));
   ME_LAUNCH_CHECK("me_embed");
   return 0;
 }

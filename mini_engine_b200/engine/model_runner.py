@@ -63,23 +63,25 @@ class _StepGraph:
         self.form: Optional[str] = None          # the decode attention form the capture was tuned to, if it was
 
 
-def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, tuple[int, int]], dict[int, StateNeed]]:
-    """Group the model's cache slots by what they need; returns (groups, slot -> (group, index), slot -> state)."""
+def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, tuple[int, int]], dict[int, list[StateNeed]]]:
+    """Group the model's cache slots by what they need; returns (groups, slot -> (group, index), slot -> states)."""
     keyed: dict[tuple, list[int]] = {}
-    states: dict[int, StateNeed] = {}
+    states: dict[int, list[StateNeed]] = {}
     for slot, needs in enumerate(model.slot_needs):
         for need in needs:
             if isinstance(need, KVCacheNeed):
-                keyed.setdefault((need.window, need.num_kv_heads, need.head_dim), []).append(slot)
+                keyed.setdefault((need.window, need.num_kv_heads, need.head_dim, need.planes), []).append(slot)
             elif isinstance(need, StateNeed):
-                states[slot] = need
+                if any(n.name == need.name for n in states.get(slot, [])):
+                    raise ValueError(f"cache slot {slot}: two states are named {need.name!r}")
+                states.setdefault(slot, []).append(need)
             else:
                 raise TypeError(f"cache slot {slot}: unknown kind of cache need {need!r}")
     groups, location = [], {}
-    for (window, nkv, hd), slots in keyed.items():
+    for (window, nkv, hd, planes), slots in keyed.items():
         for i, s in enumerate(slots):
             location[s] = (len(groups), i)
-        groups.append(GroupSpec(window, nkv, hd, tuple(slots)))
+        groups.append(GroupSpec(window, nkv, hd, tuple(slots), planes))
     return groups, location, states
 
 
@@ -109,9 +111,9 @@ class ModelRunner:
         self.groups, self.slot_location, self.state_needs = plan_cache_groups(self.model)
         self.error_flag = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.num_state_slots = max_num_seqs if self.state_needs else 0
-        self.state_storage = {slot: torch.zeros(self.num_state_slots, *need.shape, dtype=getattr(torch, need.dtype),
-                                                device=self.device)
-                              for slot, need in self.state_needs.items()}
+        self.state_storage = {(slot, need.name): torch.zeros(self.num_state_slots, *need.shape, dtype=getattr(torch, need.dtype),
+                                                              device=self.device)
+                              for slot, needs in self.state_needs.items() for need in needs}
         # Four error flags and the tokens drawn by the last step whose results were staged here: one copy to the host,
         # and the place where a step launched ahead of the host finds the tokens it continues from (a token id ~j).
         self.result_dev = torch.zeros(4 + max_num_seqs, dtype=torch.int32, device=self.device)
@@ -147,11 +149,11 @@ class ModelRunner:
     # ---- sizes -----------------------------------------------------------------------
     def page_bytes(self) -> int:
         """Bytes of one page over all groups and their cache slots."""
-        return sum(len(g.cache_slots) * 2 * g.num_kv_heads * self.page_size * g.head_dim
+        return sum(len(g.cache_slots) * g.planes * g.num_kv_heads * self.page_size * g.head_dim
                    for g in self.groups) * self.act_dtype.itemsize
 
     def _make_pools(self, num_pages: int) -> list[torch.Tensor]:
-        return [torch.zeros(len(g.cache_slots), num_pages, 2, g.num_kv_heads, self.page_size, g.head_dim,
+        return [torch.zeros(len(g.cache_slots), num_pages, g.planes, g.num_kv_heads, self.page_size, g.head_dim,
                             dtype=self.act_dtype, device=self.device) for g in self.groups]
 
     def _size_pool(self, utilization: float) -> int:
@@ -458,9 +460,15 @@ class ModelRunner:
 
     def _capture(self, g: _StepGraph, token_ids: torch.Tensor, sample: bool) -> None:
         """Run the step once eagerly (this allocates the graph's work buffers), then capture it; both runs do the
-        step's real work."""
+        step's real work.  Keys and values written twice are the same; the state of a mixer that has some would be
+        advanced twice, so the slots of the step's requests are put back after the eager run."""
         g.ctx.frozen = False
+        slots = [s for s in (g.ctx.host.state_slots if g.ctx.host is not None else []) if s >= 0] if self.state_needs else []
+        index = torch.tensor(slots, dtype=torch.int64, device=self.device) if slots else None
+        saved = {k: t.index_select(0, index) for k, t in self.state_storage.items()} if slots else {}
         self._forward(token_ids, g.ctx, sample)
+        for k, t in saved.items():
+            self.state_storage[k].index_copy_(0, index, t)
         torch.cuda.current_stream().synchronize()
         g.ctx.frozen = True
         before = ops.launches
@@ -486,7 +494,9 @@ class ModelRunner:
         kernels and the forms lie close together; a large batch has many blocks an SM, where one form wins by rule, its
         graphs are many (narrow context buckets) and each measurement costs a tenth of a second: a workload of 256
         requests that end one after the other spent a third of its time measuring."""
-        tune = self.tune_decode_form and ops.decode_form == "auto" and g.bucket < self.tune_decode_max_bucket
+        # (a model with state is not replayed for timing: every replay would advance the state)
+        tune = (self.tune_decode_form and ops.decode_form == "auto" and g.bucket < self.tune_decode_max_bucket
+                and not self.state_needs)
         forms = ops.decode_forms_for(self.page_size) if tune else [None]
         best = None
         try:

@@ -36,7 +36,8 @@ class TraceReplayer:
         held = (max_tokens + unit - 1) // unit * unit
         num_pages = max(1, (held + page_size - 1) // page_size)
         cfg = load_model_config(model_dir)
-        args = dict(max_num_seqs=8, max_num_batched_tokens=4096, max_model_len=cfg.max_position_embeddings)
+        # no request can hold more than the pool; state slots for four live requests
+        args = dict(max_num_seqs=4, max_num_batched_tokens=4096, max_model_len=min(cfg.max_position_embeddings, held))
         args.update(runner_args)
         self.runner = ModelRunner(model_dir, dtype=dtype, page_size=page_size, num_pages=num_pages,
                                   model_config=cfg, **args)

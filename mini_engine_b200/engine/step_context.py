@@ -107,6 +107,7 @@ class StepContext:
         g, idx = self.runner.slot_location[cache_slot]
         return KVView(self.runner.kv_pools[g][idx], self.runner.page_size, self._bt[g], self._sm[g], g)
 
-    def state(self, cache_slot: int) -> torch.Tensor:
-        """Storage of a mixer's per-request state: [num_state_slots, *shape] of the dtype its ``StateNeed`` names."""
-        return self.runner.state_storage[cache_slot]
+    def state(self, cache_slot: int, name: str = "") -> torch.Tensor:
+        """Storage of a layer's per-request state: [num_state_slots, *shape] of the dtype its ``StateNeed`` names
+        (``name``: which one, for a layer that asked for several)."""
+        return self.runner.state_storage[(cache_slot, name)]

@@ -21,7 +21,15 @@ MAX_HEAD_DIM = 256
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 _PROTOS = {
-    "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _I, _P],
+    "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _I, _F, _I, _L, _P],
+    "me_hc_norm": [_P, _L, _I, _P, _I, _P, _P, _P, _P, _F, _P, _I, _P, _I, _I, _P],
+    "me_short_conv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_polynorm": [_P, _I, _L, _P, _F, _P, _I, _L, _I, _I, _P],
+    "me_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "me_mlstm_out": [_P, _P, _L, _I, _P, _F, _P, _I, _I, _I, _I, _P],
+    "me_latent_prep": [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "me_latent_attention": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "me_heads_to_rows": [_P, _P, _I, _I, _I, _I, _P],
     "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _L, _P],
     "me_gemm_skinny": [_P, _L, _P, _P, _I, _L, _P, _I, _I, _I, _I, _P],
     "me_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -229,16 +237,18 @@ def check_attention_sizes(head_dim: int, num_heads: int, num_kv_heads: int) -> N
 
 # ---- element-wise and normalisation ----------------------------------------------------
 def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor,
-          feedback: Optional[torch.Tensor] = None) -> None:
-    """Rows of ``table`` into the float32 ``out``.  An id ~j (negative) stands for ``feedback[j]`` (int32 on the
-    device: the tokens the step before drew); ids outside the vocabulary set flag 0 of ``err``."""
+          feedback: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """Rows of ``table`` times ``scale`` into the float32 ``out`` [T, H], or into every stream of ``out`` [S, T, H].
+    An id ~j (negative) stands for ``feedback[j]`` (int32 on the device: the tokens the step before drew); ids
+    outside the vocabulary set flag 0 of ``err``."""
     _need(ids.dtype == torch.int32 and ids.is_contiguous(), "embed: token ids must be contiguous int32")
     _need(feedback is None or (feedback.dtype == torch.int32 and feedback.is_contiguous()), "embed: feedback must be int32")
     _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous(), "embed: bad tensors")
     T, (V, H) = ids.shape[0], table.shape
-    _need(tuple(out.shape) == (T, H), "embed: output shape")
+    copies = out.shape[0] if out.dim() == 3 else 1
+    _need(tuple(out.shape[-2:]) == (T, H) and out.dim() in (2, 3), "embed: output shape")
     _call("me_embed", ids.data_ptr(), table.data_ptr(), _dt(table), out.data_ptr(), T, H, V, err.data_ptr(), _ptr(feedback),
-          feedback.numel() if feedback is not None else 0, _stream())
+          feedback.numel() if feedback is not None else 0, float(scale), copies, T * H, _stream())
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -970,3 +980,137 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor
     _call("me_sample", logits.data_ptr(), logits.stride(0), temperatures.data_ptr(), seeds.data_ptr(),
           positions.data_ptr(), out.data_ptr(), S, V, part[0].data_ptr(), part[1].data_ptr(), _stream())
     launches += 1
+
+
+# ---- several residual streams, layer norm, short convolutions, PolyNorm ----------------------------
+def hc_norm(streams: torch.Tensor, *, update=None, mix_in: Optional[torch.Tensor] = None,
+            norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, out: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """One pass over the residual streams ``streams`` [S, T, W] (float32): apply the pending ``update`` = (y [T, W],
+    mix [S, S] indexed [from, to], out weights [S]): x_r <- sum_s mix[s, r] x_s + out[r] y; then, with ``norm_weight``,
+    write the layer norm of u = sum_s mix_in[s] x_s (every stream once without ``mix_in``) to ``out``.  With ``rows``
+    only those tokens are read and the streams stay as they are."""
+    _need(streams.dim() == 3 and streams.dtype == torch.float32 and streams.is_contiguous(), "hc_norm: streams must be float32 [S, T, W]")
+    S, T, W = streams.shape
+    y = mix = outw = None
+    if update is not None:
+        y, mix, outw = update
+        _need(tuple(y.shape) == (T, W) and y.is_contiguous(), "hc_norm: the update's y must be [T, W]")
+        _need(mix.dtype == torch.float32 and tuple(mix.shape) == (S, S) and mix.is_contiguous()
+              and outw.dtype == torch.float32 and outw.numel() == S, "hc_norm: mix must be float32 [S, S], out weights [S]")
+    _need(mix_in is None or (mix_in.dtype == torch.float32 and mix_in.numel() == S), "hc_norm: in weights must be float32 [S]")
+    n = T if rows is None else rows.shape[0]
+    if norm_weight is not None:
+        _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == W, "hc_norm: norm weight must be float32 [W]")
+        _need(out is not None and out.is_contiguous() and tuple(out.shape) == (n, W), "hc_norm: output shape")
+    _need(rows is None or rows.dtype == torch.int32, "hc_norm: rows must be int32")
+    _call("me_hc_norm", streams.data_ptr(), T * W, S, _ptr(y), _dt(y) if y is not None else 0, _ptr(mix), _ptr(outw), _ptr(mix_in),
+          _ptr(norm_weight), float(eps), _ptr(out), _dt(out) if out is not None else 0, _ptr(rows), n, W, _stream())
+
+
+def short_conv(h: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], token_req: torch.Tensor, meta,
+               state_slots: torch.Tensor, out: torch.Tensor, add_input: bool = True) -> None:
+    """``out_t = [h_t +] sum_j weight[:, j] h_(t - taps + 1 + j)`` per channel over each request's tokens, zeros before
+    its first token; inputs from before this step come from ``state`` [slots, taps - 1, W], which then takes the
+    step's last inputs.  ``h`` [T, W], ``weight`` [W, taps] and ``state`` are float32."""
+    T, W = h.shape
+    taps = weight.shape[1]
+    _need(h.dtype == torch.float32 and h.is_contiguous() and weight.dtype == torch.float32 and weight.is_contiguous()
+          and weight.shape[0] == W, "short_conv: h [T, W] and weight [W, taps] must be float32")
+    _need(taps == 1 or (state is not None and state.dtype == torch.float32 and state.is_contiguous()
+                        and tuple(state.shape[1:]) == (taps - 1, W)), "short_conv: state must be float32 [slots, taps - 1, W]")
+    _need(out.is_contiguous() and tuple(out.shape) == (T, W), "short_conv: output shape")
+    _call("me_short_conv", h.data_ptr(), weight.data_ptr(), _ptr(state) if taps > 1 else 0, token_req.data_ptr(),
+          meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), state_slots.data_ptr(), out.data_ptr(), _dt(out), T,
+          meta.num_reqs, W, taps, 1 if add_input else 0, 1, _stream())
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = a N(z) + b N(z^2) + c N(z^3) + e`` row by row, N(v) = v / sqrt(mean(v^2) + eps); ``coef`` = (a, b, c, e)."""
+    _need(z.dim() == 2 and z.stride(1) == 1 and out.stride(1) == 1 and out.shape == z.shape, "polynorm: shapes")
+    _need(coef.dtype == torch.float32 and coef.numel() == 4, "polynorm: four float32 coefficients")
+    _call("me_polynorm", z.data_ptr(), _dt(z), z.stride(0), coef.data_ptr(), float(eps), out.data_ptr(), _dt(out),
+          out.stride(0), z.shape[0], z.shape[1], _stream())
+
+
+# ---- the matrix-memory recurrence ------------------------------------------------------------------
+def mlstm_scan(proj: torch.Tensor, offsets: dict, bias_i: torch.Tensor, bias_f: torch.Tensor, gate_cap: float,
+               S: torch.Tensor, n: torch.Tensor, m: torch.Tensor, meta, state_slots: torch.Tensor, o: torch.Tensor,
+               num_heads: int, dim: int, vdim: int, q_scale: float) -> None:
+    """Walks every request's tokens of this step through the recurrence from the state in its slot (see csrc/mlstm.cu).
+    ``proj`` [T, N] float32 holds q, k, v, i, f at the column ``offsets``; ``o`` [T, heads * vdim] float32."""
+    T = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "mlstm_scan: projections must be float32 rows")
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (S, n, m, o, bias_i, bias_f)), "mlstm_scan: float32 state")
+    _need(tuple(S.shape[1:]) == (num_heads, dim, vdim) and tuple(n.shape[1:]) == (num_heads, dim) and m.shape[1] == num_heads,
+          "mlstm_scan: state shapes")
+    _need(tuple(o.shape) == (T, num_heads * vdim), "mlstm_scan: output shape")
+    _call("me_mlstm_scan", proj.data_ptr(), proj.stride(0), offsets["q"], offsets["k"], offsets["v"], offsets["i"], offsets["f"],
+          bias_i.data_ptr(), bias_f.data_ptr(), float(gate_cap), S.data_ptr(), n.data_ptr(), m.data_ptr(),
+          meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), state_slots.data_ptr(), o.data_ptr(), meta.num_reqs,
+          num_heads, dim, vdim, float(q_scale), _stream())
+
+
+def mlstm_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              num_heads: int, vdim: int) -> None:
+    """Each head's ``o`` divided by its root mean square, times ``weight`` and the sigmoid of the gate columns of ``proj``."""
+    T = o.shape[0]
+    _need(weight.dtype == torch.float32 and weight.numel() == num_heads * vdim, "mlstm_out: weight must be float32 [heads * vdim]")
+    _need(out.is_contiguous() and tuple(out.shape) == (T, num_heads * vdim), "mlstm_out: output shape")
+    _call("me_mlstm_out", o.data_ptr(), proj.data_ptr(), proj.stride(0), off_g, weight.data_ptr(), float(eps), out.data_ptr(),
+          _dt(out), T, num_heads, vdim, _stream())
+
+
+# ---- attention through a latent --------------------------------------------------------------------
+LATENT_TILE_Q = 16        # query tokens per block of csrc/latent_attention.cu
+
+
+def latent_prep(proj: torch.Tensor, offsets: dict, c_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, rot_dims: int,
+                positions: torch.Tensor, slot_mapping: Optional[torch.Tensor], pool: torch.Tensor, q_plain: torch.Tensor,
+                q_rot: torch.Tensor, gate: Optional[torch.Tensor], num_heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
+    """From the packed float32 projections: the normed latent and the rotated shared key part into the cache rows named by
+    ``slot_mapping``, the heads' plain and rotated query parts, the sigmoid of the gates (see csrc/latent_attention.cu)."""
+    T = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "latent_prep: projections must be float32 rows")
+    _need(inv_freq.dtype == torch.float64 and inv_freq.numel() * 2 == rot_dims, "latent_prep: inv_freq must be float64 [rot_dims / 2]")
+    _need(pool.is_contiguous() and pool.shape[-1] == kv_rank + rot_dim and pool.dtype == q_plain.dtype == q_rot.dtype,
+          "latent_prep: cache rows must hold kv_rank + rot_dim values of the activations' dtype")
+    _need(c_weight.dtype == torch.float32 and c_weight.numel() == kv_rank, "latent_prep: latent weight must be float32 [kv_rank]")
+    _call("me_latent_prep", proj.data_ptr(), proj.stride(0), offsets["q"], offsets["c"], offsets.get("g", 0), c_weight.data_ptr(),
+          float(eps), inv_freq.data_ptr(), rot_dims, positions.data_ptr(), _ptr(slot_mapping), pool.data_ptr(), q_plain.data_ptr(),
+          q_rot.data_ptr(), _ptr(gate), _dt(pool), T, num_heads, dim, rot_dim, kv_rank, _stream())
+
+
+def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, page_size: int, block_tables: torch.Tensor,
+                     meta, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor, scale: float) -> None:
+    """Causal multi-query attention over cache rows [c | rotated key part]: ``q_abs`` [H, T, C] against c, ``q_rot``
+    [T, H, R] against the rest; ``out`` [H, T, C] = softmax-weighted sum of c (with ``sink`` [H] in the denominator),
+    times ``gate`` [T, H]."""
+    H, T, C = q_abs.shape
+    R = q_rot.shape[2]
+    _need(q_abs.is_contiguous() and q_rot.is_contiguous() and out.is_contiguous() and out.shape == q_abs.shape, "latent_attention: shapes")
+    _need(pool.shape[-1] == C + R and pool.dtype == q_abs.dtype, "latent_attention: cache rows")
+    tiles, n_tiles = meta.tile_lists[LATENT_TILE_Q]
+    _call("me_latent_attention", q_abs.data_ptr(), q_rot.data_ptr(), _dt(q_abs), pool.data_ptr(), block_tables.data_ptr(),
+          block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles,
+          meta.num_decodes, _ptr(sink), _ptr(gate), out.data_ptr(), T, H, C, R, page_size, float(scale), _stream())
+
+
+def heads_to_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """[H, T, V] -> [T, H * V]."""
+    H, T, V = x.shape
+    _need(x.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, H * V) and out.dtype == x.dtype, "heads_to_rows: shapes")
+    _call("me_heads_to_rows", x.data_ptr(), out.data_ptr(), _dt(x), T, H, V, _stream())
+
+
+def batched_heads_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[h] = x[h] @ w[h]`` for every head: [H, T, K] x [H, K, N] -> [H, T, N], through the library's batched product
+    (either operand may be a strided view).  float32 operands are multiplied in true 32-bit."""
+    global library_calls
+    _need(x.dim() == 3 and w.dim() == 3 and x.shape[0] == w.shape[0] and x.shape[2] == w.shape[1], "batched_heads_mm: shapes")
+    _need(x.dtype == w.dtype == out.dtype, "batched_heads_mm: one dtype")
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("batched_heads_mm: TF32 is switched on for float32 products; the float32 engine needs it off")
+    with _Timed("library_bmm"):
+        torch.bmm(x, w, out=out)
+    library_calls += 1

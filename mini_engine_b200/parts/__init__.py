@@ -1,12 +1,16 @@
 from .base import (AddedToResidual, PendingNorm, Upcoming, DiskSource, FeedForward, KVCacheNeed, Mixer, Norm, ParamDecl, Part,
-                   PositionEncoding, StateNeed)
+                   PositionEncoding, StateNeed, StreamUpdate)
 from .registry import (PartSpec, build_block, build_part, register_block, register_feed_forward, register_mixer,
                        register_norm, register_position_encoding, registered)
-from .norm import RMSNorm
-from .rope import RotaryEmbedding
+from .norm import LayerNorm, RMSNorm
+from .rope import InterleavedRotary, RotaryEmbedding
 from .linear import Linear
 from .attention import GQAAttention
 from .mlp import SwiGLU
+from .conv import CausalShortConv
+from .polynorm_mlp import PolyNormMLP
+from .latent_attention import LatentAttention
+from .mlstm import MLSTM
 from .embed import LMHead, TokenEmbedding
-from .block import Block, BlockSpec, PreNormBlock, SharedRef
+from .block import Block, BlockSpec, HyperConnectionBlock, PreNormBlock, SharedRef
 from .model import DecoderModel, LayerCall, ModelPlan

@@ -36,7 +36,7 @@ class DiskSource:
 class ParamDecl:
     name: str                              # local name; the owner's prefix is put in front
     shape: tuple[int, ...]
-    init: str = "normal"                   # "normal": N(0, 0.02); "norm": 1 + N(0, 0.1)
+    init: str = "normal"                   # "normal": N(0, 0.02); "norm": 1 + N(0, 0.1); "eye": identity + N(0, 0.1)
     sources: list[DiskSource] = field(default_factory=list)   # empty: one tensor, same name
     role: str = "matrix"                   # "matrix" | "vector" (vectors are held in float32)
     tied_to: Optional[str] = None          # full name of the parameter whose storage is shared
@@ -44,17 +44,31 @@ class ParamDecl:
 
 @dataclass(frozen=True)
 class KVCacheNeed:
-    """Paged keys and values: ``window=None`` keeps every key, else the last ``window``."""
+    """Paged keys and values: ``window=None`` keeps every key, else the last ``window``.  ``planes``: 2 for keys and
+    values, 1 for a cache with one row per token and head (a latent that serves as both)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """A slot of fixed size per request: ``shape`` elements of ``dtype`` (a torch dtype's name)."""
+    """A slot of fixed size per request: ``shape`` elements of ``dtype`` (a torch dtype's name).  A layer may ask for
+    several; each then has a ``name`` of its own, by which ``StepContext.state(cache_slot, name)`` finds it."""
     shape: tuple[int, ...]
     dtype: str = "float32"
+    name: str = ""
+
+
+@dataclass
+class StreamUpdate:
+    """What a block of a model with several residual streams returns instead of a plain output: ``y`` [T, width] has
+    not been put into the streams yet; the next kernel that reads them (the next block's first norm, or the model's
+    last) first computes x_r <- sum_s mix[s, r] x_s + out[r] y for all streams r at once."""
+    y: "torch.Tensor"
+    mix: "torch.Tensor"          # [streams, streams] float32, indexed [from, to]
+    out: "torch.Tensor"          # [streams] float32
 
 
 @dataclass

@@ -7,10 +7,10 @@ used here: a block receives the residual stream and the previous sub-layer's out
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Optional
+from dataclasses import dataclass, field
+from typing import Any, Optional
 
-from .base import Part, Upcoming
+from .base import ParamDecl, Part, StreamUpdate, Upcoming
 from .registry import PartSpec, build_part, register_block
 
 
@@ -20,7 +20,7 @@ class BlockSpec:
 
     ``norm`` is the norm of both places; ``mixer_norm`` / ``feed_forward_norm`` give a place a norm of its own."""
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]   # None: a layer without a feed-forward (for block kinds that allow it)
     norm: Optional[PartSpec] = None
     mixer_norm: Optional[PartSpec] = None
     feed_forward_norm: Optional[PartSpec] = None
@@ -29,6 +29,7 @@ class BlockSpec:
     feed_forward_prefix: str = "mlp."
     mixer_norm_prefix: str = "input_layernorm."
     feed_forward_norm_prefix: str = "post_attention_layernorm."
+    args: dict[str, Any] = field(default_factory=dict)   # what the block kind itself needs (streams, taps, ...)
 
     def norm_of(self, place: str) -> PartSpec:
         spec = getattr(self, place) or self.norm
@@ -60,15 +61,26 @@ class Block(Part):
                     for k, v in mixer_spec.args.items()}
             mixer_spec = PartSpec(mixer_spec.kind, args)
         self.mixer = build_part("mixer", mixer_spec)
-        self.feed_forward = build_part("feed_forward", spec.feed_forward)
         self.mixer_norm = build_part("norm", spec.norm_of("mixer_norm"))
-        self.feed_forward_norm = build_part("norm", spec.norm_of("feed_forward_norm"))
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", spec.feed_forward)
+            self.feed_forward_norm = build_part("norm", spec.norm_of("feed_forward_norm"))
+        elif not self.feed_forward_optional:
+            raise ValueError(f"a {spec.kind!r} block needs a feed-forward")
+
+    feed_forward_optional = False
 
     def sub_parts(self):
         s = self.spec
-        return [(s.mixer_norm_prefix, self.mixer_norm), (s.mixer_prefix, self.mixer),
-                (s.feed_forward_norm_prefix, self.feed_forward_norm),
-                (s.feed_forward_prefix, self.feed_forward)]
+        parts = [(s.mixer_norm_prefix, self.mixer_norm), (s.mixer_prefix, self.mixer)]
+        if self.feed_forward is not None:
+            parts += [(s.feed_forward_norm_prefix, self.feed_forward_norm), (s.feed_forward_prefix, self.feed_forward)]
+        return parts
+
+    def cache_needs(self):
+        """What one call of this block needs of the cache: the mixer's needs, and the block's own if it has any."""
+        return self.mixer.cache_needs()
 
     def upcoming(self) -> Upcoming:
         return Upcoming()
@@ -103,6 +115,61 @@ class PreNormBlock(Block):
         return ffn.forward(x, ctx)
 
 
+class HyperConnectionBlock(Block):
+    """A pre-norm block over several residual streams, with a short convolution in front of each sub-layer.
+
+    The model keeps ``streams`` copies x_1 .. x_S of the residual stream ([S, T, width] float32).  Sub-layer q (1: mixer,
+    2: feed-forward) reads u = sum_s in_q[s] x_s, computes y = sublayer(h + conv_q(h)) with h = norm_q(u) and
+    conv_q a causal convolution of ``taps`` taps over time on each channel, and all streams are renewed at once:
+    x_r <- sum_s mix_q[s, r] x_s + out_q[r] y.  That last step is left to the kernel that reads the streams next (the
+    following norm), so a block returns its last y as a ``StreamUpdate``.  The block's own parameters are
+    ``hc1.in / hc1.out / hc1.mix`` (and ``hc2.*``) and the convolutions ``canon1`` / ``canon2``, whose last inputs are
+    part of a request's state.  The feed-forward may be absent.
+
+    ``BlockSpec.args``: ``streams``, ``width``, ``taps``."""
+    capturable = True
+    feed_forward_optional = True
+
+    def __init__(self, spec: BlockSpec, shared: Optional[dict] = None):
+        super().__init__(spec, shared)
+        from .conv import CausalShortConv
+        self.streams = int(spec.args["streams"])
+        self.width = int(spec.args["width"])
+        taps = int(spec.args["taps"])
+        self.conv1 = CausalShortConv(self.width, taps, param="canon1", state_name="canon1")
+        self.conv2 = CausalShortConv(self.width, taps, param="canon2", state_name="canon2") if self.feed_forward is not None else None
+
+    def sub_parts(self):
+        parts = super().sub_parts() + [("", self.conv1)]
+        if self.conv2 is not None:
+            parts.append(("", self.conv2))
+        return parts
+
+    def param_decls(self):
+        S = self.streams
+        decls = []
+        for q in ("hc1", "hc2") if self.feed_forward is not None else ("hc1",):
+            decls += [ParamDecl(q + ".in", (S,), init="norm", role="vector"), ParamDecl(q + ".out", (S,), init="norm", role="vector"),
+                      ParamDecl(q + ".mix", (S, S), init="eye", role="vector")]
+        return decls
+
+    def cache_needs(self):
+        needs = self.mixer.cache_needs() + self.conv1.cache_needs()
+        return needs + (self.conv2.cache_needs() if self.conv2 is not None else [])
+
+    def forward(self, residual, delta, ctx, call, upcoming=None):
+        """``residual`` [streams, T, width]; ``delta``: the ``StreamUpdate`` the block before left (or None)."""
+        import torch
+        h = self.mixer_norm.forward(residual, delta, ctx, mix_in=self.p("hc1.in"), out_dtype=torch.float32, out_name="norm_h")
+        y = self.mixer.forward(self.conv1.forward(h, ctx, call.cache_slot), ctx, call)
+        update = StreamUpdate(y, self.p("hc1.mix"), self.p("hc1.out"))
+        if self.feed_forward is None:
+            return update
+        h = self.feed_forward_norm.forward(residual, update, ctx, mix_in=self.p("hc2.in"), out_dtype=torch.float32, out_name="norm_h")
+        y = self.feed_forward.forward(self.conv2.forward(h, ctx, call.cache_slot), ctx)
+        return StreamUpdate(y, self.p("hc2.mix"), self.p("hc2.out"))
+
+
 @dataclass(frozen=True)
 class SharedRef:
     """Stands in a PartSpec's args for an object that the model builds once and shares."""
@@ -110,3 +177,4 @@ class SharedRef:
 
 
 register_block("pre_norm", PreNormBlock)
+register_block("hyper_connection", HyperConnectionBlock)

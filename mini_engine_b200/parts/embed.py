@@ -15,34 +15,40 @@ from .base import ParamDecl, Part
 class TokenEmbedding(Part):
     capturable = True
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, streams: int = 1, param: str = "weight"):
         super().__init__()
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
+        self.scale = float(scale)          # rows are multiplied by this
+        self.streams = streams             # > 1: the residual is [streams, T, hidden], every stream the embedding
+        self.param = param
 
     def param_decls(self):
-        return [ParamDecl("weight", (self.vocab_size, self.hidden_size))]
+        return [ParamDecl(self.param, (self.vocab_size, self.hidden_size))]
 
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
-        out = ctx.buffer("residual", (token_ids.shape[0], self.hidden_size), torch.float32)
-        ops.embed(token_ids, self.p("weight"), out, ctx.error_flag, feedback=getattr(ctx, "token_feedback", None))
+        shape = (token_ids.shape[0], self.hidden_size)
+        out = ctx.buffer("residual", shape if self.streams == 1 else (self.streams, *shape), torch.float32)
+        ops.embed(token_ids, self.p(self.param), out, ctx.error_flag, feedback=getattr(ctx, "token_feedback", None),
+                  scale=self.scale)
         return out
 
 
 class LMHead(Part):
     capturable = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None, param: str = "weight"):
         super().__init__()
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
+        self.param = param
 
     def param_decls(self):
-        return [ParamDecl("weight", (self.vocab_size, self.hidden_size), tied_to=self.tied_to)]
+        return [ParamDecl(self.param, (self.vocab_size, self.hidden_size), tied_to=self.tied_to)]
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
         ops.tag = "logits"
-        ops.linear(x, self.p("weight"), out, workspace=ctx.buffer, err=ctx.error_flag)
+        ops.linear(x, self.p(self.param), out, workspace=ctx.buffer, err=ctx.error_flag)
         return out

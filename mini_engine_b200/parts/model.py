@@ -42,6 +42,10 @@ class ModelPlan:
     block_prefix: str = "model.layers.{i}."
     final_norm_prefix: str = "model.norm."
     head_prefix: str = "lm_head."
+    embed_param: str = "weight"        # the tensors' names behind those prefixes
+    head_param: str = "weight"
+    embedding_scale: float = 1.0       # the embedding's rows are multiplied by this
+    streams: int = 1                   # residual streams; > 1: the residual is [streams, T, hidden], all equal at the start
 
 
 class DecoderModel(Part):
@@ -51,11 +55,12 @@ class DecoderModel(Part):
         super().__init__()
         self.plan = plan
         self.shared = {k: build_part("position_encoding", s) for k, s in plan.shared.items()}
-        self.embed = TokenEmbedding(plan.vocab_size, plan.hidden_size)
+        self.embed = TokenEmbedding(plan.vocab_size, plan.hidden_size, scale=plan.embedding_scale, streams=plan.streams,
+                                    param=plan.embed_param)
         self.blocks = [build_block(s, self.shared) for s in plan.blocks]
         self.final_norm = build_part("norm", plan.final_norm)
-        tied = plan.embed_prefix + "weight" if plan.tie_word_embeddings else None
-        self.head = LMHead(plan.vocab_size, plan.hidden_size, tied)
+        tied = plan.embed_prefix + plan.embed_param if plan.tie_word_embeddings else None
+        self.head = LMHead(plan.vocab_size, plan.hidden_size, tied, param=plan.head_param)
         self.schedule = list(plan.schedule)
         n_slots = 1 + max((c.cache_slot for c in self.schedule), default=-1)
         # What each cache slot must hold, taken from the first call that uses it.
@@ -64,7 +69,7 @@ class DecoderModel(Part):
         for c in self.schedule:
             if not 0 <= c.block < len(self.blocks):
                 raise ValueError(f"schedule names block {c.block}, the model has {len(self.blocks)}")
-            needs = self.blocks[c.block].mixer.cache_needs()
+            needs = self.blocks[c.block].cache_needs()
             if not self.slot_needs[c.cache_slot]:
                 self.slot_needs[c.cache_slot] = needs
             elif self.slot_needs[c.cache_slot] != needs:

@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import AddedToResidual, Norm, ParamDecl, PendingNorm
+from .base import AddedToResidual, Norm, ParamDecl, PendingNorm, StreamUpdate
 from .registry import register_norm
 
 
@@ -44,4 +44,44 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w`` with var the mean squared deviation, a weight and no bias, over one
+    residual stream or several: with ``streams`` > 1 the residual is [streams, T, size] and the norm reads
+    u = sum_s mix_in[s] x_s (every stream once when no ``mix_in`` is given: the sum of the streams).  A pending
+    ``StreamUpdate`` (or, with one stream, a plain output still to be added) goes into the streams in the same pass.
+    ``param``: the weight's name on disk, for models that do not call it ``weight``."""
+    capturable = True
+
+    def __init__(self, size: int, eps: float, streams: int = 1, param: str = "weight"):
+        super().__init__()
+        self.size = size
+        self.eps = float(eps)
+        self.streams = streams
+        self.param = param
+        self._ones = None
+
+    def param_decls(self):
+        return [ParamDecl(self.param, (self.size,), init="norm", role="vector")]
+
+    def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False, *,
+                mix_in: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, out_name: str = "norm_out"):
+        streams = residual if residual.dim() == 3 else residual.unsqueeze(0)
+        update = None
+        if isinstance(delta, StreamUpdate):
+            update = (delta.y, delta.mix, delta.out)
+        elif isinstance(delta, AddedToResidual):
+            delta = None
+        elif delta is not None:
+            if delta.dim() == 3 or streams.shape[0] != 1:
+                raise ValueError("LayerNorm: a plain output can only be added to a single residual stream")
+            if self._ones is None:
+                self._ones = torch.ones(1, 1, dtype=torch.float32, device=residual.device)
+            update = (delta, self._ones, self._ones.view(1))
+        n = streams.shape[1] if rows is None else rows.shape[0]
+        out = ctx.buffer(out_name, (n, self.size), out_dtype or ctx.act_dtype)
+        ops.hc_norm(streams, update=update, mix_in=mix_in, norm_weight=self.p(self.param), eps=self.eps, out=out, rows=rows)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

@@ -37,4 +37,28 @@ class RotaryEmbedding(PositionEncoding):
         self.cos_sin = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(device)
 
 
+class InterleavedRotary(PositionEncoding):
+    """Rotary positions on pairs of neighbouring elements: (x[2i], x[2i+1]) at position p becomes
+    (u cos a - v sin a, v cos a + u sin a) with a = p * theta^(-2i / rotary_dim), on the first ``rotary_dim`` elements.
+    It keeps no table over positions: the kernels form each angle from the position and ``inv_freq`` (float64, so that
+    the angle is rounded once, to the float32 cosine and sine), which leaves the longest position open."""
+    capturable = True
+
+    layout = "interleaved"
+
+    def __init__(self, rotary_dim: int, theta: float):
+        super().__init__()
+        if rotary_dim % 2 or rotary_dim < 0:
+            raise ValueError(f"rotary_dim {rotary_dim} must be even")
+        self.rotary_dim = rotary_dim
+        self.theta = float(theta)
+        self.inv_freq: torch.Tensor | None = None
+
+    def finalize(self, dtype, device):
+        d = self.rotary_dim
+        i = torch.arange(0, d, 2, dtype=torch.float64)
+        self.inv_freq = (self.theta ** (-i / d) if d else i).contiguous().to(device)
+
+
 register_position_encoding("rope", RotaryEmbedding)
+register_position_encoding("rope_interleaved", InterleavedRotary)

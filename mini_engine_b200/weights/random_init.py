@@ -42,7 +42,10 @@ def random_state_dict(model: DecoderModel, seed: int, dtype: torch.dtype = torch
     out: dict[str, torch.Tensor] = {}
     for name, e in expected_disk_tensors(model).items():
         x = torch.randn(e.shape, generator=gen, dtype=torch.float32)
-        x = 1.0 + norm_std * x if init_of[name] == "norm" else matrix_std * x
+        if init_of[name] == "eye":
+            x = torch.eye(e.shape[0], e.shape[1]) + norm_std * x
+        else:
+            x = 1.0 + norm_std * x if init_of[name] == "norm" else matrix_std * x
         out[name] = x.to(dtype).contiguous()
     return out
 
@@ -82,7 +85,10 @@ def init_random_on_device(model: DecoderModel, seed: int, dtype: torch.dtype, de
             continue
         if decl.role == "vector":
             t = torch.empty(decl.shape, dtype=torch.float32, device=device).normal_(0.0, 1.0, generator=gen)
-            t = t.mul_(norm_std).add_(1.0) if decl.init == "norm" else t.mul_(matrix_std)
+            if decl.init == "eye":
+                t = t.mul_(norm_std).add_(torch.eye(decl.shape[0], decl.shape[1], device=device))
+            else:
+                t = t.mul_(norm_std).add_(1.0) if decl.init == "norm" else t.mul_(matrix_std)
         else:
             t = torch.empty(decl.shape, dtype=dtype, device=device).normal_(0.0, matrix_std, generator=gen)
             if decl.init == "norm":
