@@ -28,7 +28,8 @@ GPU: for ``--gpus N`` with N > 1 one line says so and the exit code is 2.
 Modes: ``step`` (the line above), ``offline`` (the reference's own bench.py:38-66 with its options ``--num-seqs
 --budget --chunked --threshold --out --label --expect-gpu``; a JSON row like the reference's is appended to
 ``--out``), ``mixed`` (the 8B workload above, at any shape), ``decode`` (decode at batches ``--batches`` after
-``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``).
+``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen`` (prefill and decode of the
+Logozen design at the layer sizes ``--sizes``, beside the Qwen3 of equal size, with the time of every kernel).
 """
 from __future__ import annotations
 
@@ -63,6 +64,27 @@ SHAPES = {   # layer sizes of the Qwen3 dense models
     "32b": _qwen3(64, 5120, 64, 8, 25600, False),
 }
 SHAPE_NAMES = {"0.6b": "Qwen3-0.6B", "8b": "Qwen3-8B", "32b": "Qwen3-32B"}
+
+
+def _logozen(width, layers, ff, heads, dim, rot_dim, vdim, kv_rank, r_heads, r_dim, r_vdim, vocab=32768, streams=4, taps=4):
+    """A Logozen of ``layers`` layers, every third one the recurrence, and the Qwen3 of the same width, depth, heads,
+    feed-forward width and vocabulary (its head size: dim + rot_dim) to set beside it."""
+    att = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+                     "rot": {"base": 10000.0, "dims": rot_dim}, "scale": (dim + rot_dim) ** -0.5}}
+    rec = {"type": "mlstm", "mlp": {"kind": "dense", "ff": ff},
+           "mixer": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "gate_cap": 15.0}}
+    cfg = {"architecture": "Logozen", "vocab": vocab, "width": width, "streams": streams, "canon": {"taps": taps},
+           "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": [rec if i % 3 == 0 else att for i in range(layers)]}
+    twin = _qwen3(layers, width, heads, max(heads // 2, 1), ff, False, head_dim=dim + rot_dim, vocab_size=vocab)
+    return cfg, twin
+
+
+LOGOZEN_SIZES = {   # width, layers, ff, attention heads / dim / rot_dim / vdim / kv_rank, recurrence heads / dim / vdim
+    "s": _logozen(1024, 8, 3072, 16, 32, 32, 64, 128, 8, 64, 128),
+    "m": _logozen(2048, 8, 8192, 16, 64, 64, 128, 256, 8, 128, 256),
+    "l": _logozen(4096, 6, 12288, 32, 64, 64, 128, 512, 16, 128, 256),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
@@ -72,7 +94,8 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill"], default="step")
+    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen"], default="step")
+    p.add_argument("--sizes", default="s,m", help="logozen mode: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
     p.add_argument("--shape", choices=sorted(SHAPES), default="0.6b", help="layer sizes, when no --model is given")
     p.add_argument("--extras", type=int, default=1,
                    help="step mode: also run the offline workload, the 8B mixed workload and the 32B decode points")
@@ -167,6 +190,18 @@ class Model:
         self.layers = self.cfg["num_hidden_layers"]
         self.vocab = self.cfg["vocab_size"]
         self.default_context = 4096 if self.cfg["hidden_size"] <= 1024 else 8192
+
+    @classmethod
+    def of_config(cls, cfg: dict, name: str, seed: int) -> "Model":
+        """A configuration given as a dict, its weights drawn on the device."""
+        m = cls.__new__(cls)
+        m.cfg, m.name = cfg, name
+        m.folder = model_folder(cfg, seed, weights=False)
+        m.engine_args = {"random_weights": True}
+        m.layers = m.full_layers = len(cfg["layers"]) if "layers" in cfg else cfg["num_hidden_layers"]
+        m.vocab = cfg.get("vocab_size", cfg.get("vocab"))
+        m.default_context = 4096
+        return m
 
 
 class ClockSampler:
@@ -581,6 +616,111 @@ def run_prefill_mode(args) -> int:
     return 0
 
 
+# ---- the Logozen design beside the Qwen3 of equal size ------------------------------------------------------------------
+def _kernel_times(runner, cache, prompt, batch_prompts) -> dict:
+    """One prefill step of ``prompt`` and one decode step of ``batch_prompts`` launched kernel by kernel, every launch
+    between two CUDA events: microseconds per entry point, summed over the step."""
+    import torch
+    from mini_engine_b200 import ops
+    from mini_engine_b200.cache.manager import CacheHolder
+    from mini_engine_b200.engine.model_runner import StepItem
+    graphs, runner.use_cuda_graphs = runner.use_cuda_graphs, False
+    out = {}
+    try:
+        holders = prefill_requests(runner, cache, batch_prompts, 8)
+        h = CacheHolder()
+        assert cache.allocate(h, len(prompt))
+        steps = {"prefill": [StepItem(h, prompt, 0, [len(prompt) - 1])],
+                 "decode": [StepItem(x, [5], len(p), [0], (0.6, i)) for i, (x, p) in enumerate(zip(holders, batch_prompts))]}
+        for what, items in steps.items():
+            runner.step(items, sample=True)                       # once untimed
+            torch.cuda.synchronize()
+            ops.timeline = []
+            runner.step(items, sample=True)
+            torch.cuda.synchronize()
+            tl, ops.timeline = ops.timeline, None
+            acc = {}
+            for _tag, name, e0, e1 in tl:
+                t = acc.setdefault(name, [0.0, 0])
+                t[0] += e0.elapsed_time(e1) * 1e3
+                t[1] += 1
+            out[what] = {k: {"us": round(v[0], 1), "launches": v[1]} for k, v in sorted(acc.items(), key=lambda kv: -kv[1][0])}
+        for x in holders + [h]:
+            cache.free(x)
+    finally:
+        ops.timeline = None
+        runner.use_cuda_graphs = graphs
+    return out
+
+
+def _logozen_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
+    """What the design's own kernels have to move or do in a prefill step of T tokens, and the fraction of the measured
+    peak that their summed time makes: bytes for the element-wise kernels, multiply-adds for attention and recurrence."""
+    W, S = cfg["width"], cfg["streams"]
+    need = {"me_hc_norm": 0.0, "me_short_conv": 0.0, "me_polynorm": 0.0, "me_latent_attention": 0.0, "me_mlstm_scan": 0.0}
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        subs = 2 if layer["mlp"] is not None else 1
+        need["me_hc_norm"] += subs * T * W * (8 * S + item + 4)            # streams read and written, y read, h written
+        need["me_short_conv"] += subs * T * W * (4 + item)
+        if layer["mlp"] is not None:
+            need["me_polynorm"] += T * layer["mlp"]["ff"] * (4 + item)
+        if layer["type"] == "latent_attention":
+            need["me_latent_attention"] += 2.0 * m["heads"] * (2 * m["kv_rank"] + m["rot_dim"]) * T * (T + 1) / 2
+        else:
+            need["me_mlstm_scan"] += 4.0 * m["heads"] * m["dim"] * m["vdim"] * T
+    need["me_hc_norm"] += W * (4 * S + item)                               # the last norm, one row
+    out = {}
+    for name, amount in need.items():
+        us = times.get(name, {}).get("us")
+        if not us or not amount:
+            continue
+        flops = name in ("me_latent_attention", "me_mlstm_scan")
+        rate = amount / (us * 1e-6)
+        out[name] = {"us": us, ("flops" if flops else "bytes"): amount,
+                     "frac": round(rate / (pk["bf16_tflops"] * 1e12 if flops else pk["hbm_gbs"] * 1e9), 4),
+                     "of": "bf16_tflops" if flops else "hbm_gbs"}
+    return out
+
+
+def run_logozen_mode(args) -> int:
+    """Prefill and decode throughput of Logozen at layer sizes that resemble real models', beside the Qwen3 of the same
+    width, depth, heads, feed-forward width and vocabulary; random weights drawn on the device."""
+    import torch
+    pk = peaks()
+    item = 2 if args.dtype in ("bfloat16", "bf16") else 4
+    T = args.prompt_len or 2048
+    batches = [int(b) for b in args.batches.split(",") if b]
+    rows = {}
+    for size in [x for x in args.sizes.split(",") if x]:
+        cfg, twin = LOGOZEN_SIZES[size]
+        for label, c in (("logozen", cfg), ("qwen3", twin)):
+            model = Model.of_config(c, f"{label} {size}", args.seed)
+            top = max(batches)
+            llm = make_engine(model, args, max_seqs=max(top, 4), budget=max(T, top), context=T + 256,
+                              pages=(top + 2) * ((T + 128) // args.page_size + 2), enable_prefix_caching=False)
+            runner, cache = llm.model_runner, llm.cache
+            prompts = random_prompts(top, T // 2, model.vocab, args.seed + 1)
+            (prompt,) = random_prompts(1, T, model.vocab, args.seed + 2)
+            ms = prefill_on_device(runner, cache, prompt, reps=max(3, min(args.steps, 10)), warmup=args.warmup)
+            row = {"prefill": {"tokens": T, "ms": round(ms, 3), "tok_s": round(T * 1000.0 / ms, 1)}}
+            for b in batches:
+                dms, _, _ = decode_on_device(runner, cache, prompts[:b], max(10, min(args.steps, 50)), max(3, args.warmup))
+                row[f"decode_b{b}"] = {"ms_per_step": round(dms, 4), "tok_s": round(b * 1000.0 / dms, 1)}
+            times = _kernel_times(runner, cache, prompt, prompts[:min(8, top)])
+            row["kernels_prefill_us"] = times["prefill"]
+            row["kernels_decode_b8_us"] = times["decode"]
+            if label == "logozen":
+                row["roofline_prefill"] = _logozen_roofline(c, T, item, pk, times["prefill"])
+            rows[f"{label}_{size}"] = row
+            del llm, runner, cache
+            release_memory()
+    print(json.dumps({"mode": "logozen", "dtype": args.dtype, "peaks": pk["source"], "prompt_tokens": T,
+                      "decode_context": T // 2, "sizes": {k: {"logozen": v[0], "qwen3": v[1]} for k, v in LOGOZEN_SIZES.items()
+                                                          if k in args.sizes.split(",")}, "results": rows}))
+    return 0
+
+
 # ---- the contract line -----------------------------------------------------------------------------------------------
 def run_step_mode(args) -> int:
     from mini_engine_b200 import ops
@@ -809,6 +949,8 @@ def main() -> int:
         return run_decode_mode(args)
     if args.mode == "prefill":
         return run_prefill_mode(args)
+    if args.mode == "logozen":
+        return run_logozen_mode(args)
     return run_step_mode(args)
 
 

@@ -30,6 +30,8 @@ _PROTOS = {
     "me_latent_prep": [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "me_latent_attention": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "me_heads_to_rows": [_P, _P, _I, _I, _I, _I, _P],
+    "me_latent_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "me_latent_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _L, _P],
     "me_gemm_skinny": [_P, _L, _P, _P, _I, _L, _P, _I, _I, _I, _I, _P],
     "me_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -86,6 +88,8 @@ def require_extension() -> ctypes.CDLL:
     lib.me_gemm_stream_w_box_rows.argtypes = [_I]
     lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
+    lib.me_latent_attention_mma_takes.argtypes = [_I, _I]
+    lib.me_latent_attention_mma_heads_per_block.argtypes = [_I]
     _lib = lib
     return lib
 
@@ -1063,6 +1067,17 @@ def mlstm_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, weight: torch.Ten
 
 # ---- attention through a latent --------------------------------------------------------------------
 LATENT_TILE_Q = 16        # query tokens per block of csrc/latent_attention.cu
+use_latent_mma = True     # bfloat16 latent attention on the tensor cores (csrc/latent_attention_mma.cu); a switch for comparisons
+
+
+def latent_decode_plan(num_requests: int, num_heads: int, kv_rank: int, max_context: int) -> tuple[int, int]:
+    """Into how many ranges of keys a single-token request is cut, and how long they are (a multiple of 64): enough blocks
+    to give every multiprocessor two, no range shorter than 64 keys.  A block serves 64 heads and 128 latent columns."""
+    blocks_per_range = num_requests * ((num_heads + 63) // 64) * ((kv_rank + 127) // 128)
+    tiles = max(1, (max_context + 63) // 64)
+    want = max(1, min(tiles, (2 * sm_count() + blocks_per_range - 1) // blocks_per_range))
+    keys = (tiles + want - 1) // want * 64
+    return (tiles * 64 + keys - 1) // keys, keys
 
 
 def latent_prep(proj: torch.Tensor, offsets: dict, c_weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, rot_dims: int,
@@ -1090,6 +1105,23 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tenso
     R = q_rot.shape[2]
     _need(q_abs.is_contiguous() and q_rot.is_contiguous() and out.is_contiguous() and out.shape == q_abs.shape, "latent_attention: shapes")
     _need(pool.shape[-1] == C + R and pool.dtype == q_abs.dtype, "latent_attention: cache rows")
+    lib = _lib or require_extension()
+    if q_abs.dtype == torch.bfloat16 and use_latent_mma and lib.me_latent_attention_mma_takes(C, R):
+        # the tensor-core kernels of csrc/latent_attention_mma.cu
+        gp = lib.me_latent_attention_mma_heads_per_block(H)
+        tiles, n_tiles = meta.tile_lists[64 // gp]
+        common = (q_abs.data_ptr(), q_rot.data_ptr(), pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+                  meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr())
+        if n_tiles:
+            _call("me_latent_attention_mma", *common, tiles.data_ptr(), n_tiles, _ptr(sink), _ptr(gate), out.data_ptr(), T, H, C, R,
+                  page_size, float(scale), _stream())
+        D = meta.num_decodes
+        if D:
+            splits, keys = latent_decode_plan(D, H, C, meta.max_context_len)
+            partial = meta.workspace("latent_partials", (D, splits, H, C + 2), torch.float32)
+            _call("me_latent_attention_decode", *common, D, _ptr(sink), _ptr(gate), out.data_ptr(), partial.data_ptr(), splits, keys,
+                  T, H, C, R, page_size, float(scale), _stream())
+        return
     tiles, n_tiles = meta.tile_lists[LATENT_TILE_Q]
     _call("me_latent_attention", q_abs.data_ptr(), q_rot.data_ptr(), _dt(q_abs), pool.data_ptr(), block_tables.data_ptr(),
           block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles,

@@ -23,11 +23,14 @@ def _meta(lens, contexts):
     assert all(n == 1 for n in lens[:sum(1 for n in lens if n == 1)])
     cu = np.concatenate(([0], np.cumsum(lens))).astype(np.int32)
     D = sum(1 for n in lens if n == 1)
-    tiles = [(b, q0) for b in range(D, len(lens)) for q0 in range(0, lens[b], 16)]
-    tl = torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV)
     token_req = torch.tensor(np.repeat(np.arange(len(lens)), lens), dtype=torch.int32, device=DEV)
+    lists = {}
+    for tq in (8, 16, 32, 64):
+        tiles = [(b, q0) for b in range(D, len(lens)) for q0 in range(0, lens[b], tq)]
+        lists[tq] = (torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV), len(tiles))
     return SimpleNamespace(cu_seqlens=torch.tensor(cu, device=DEV), context_lens=torch.tensor(contexts, dtype=torch.int32, device=DEV),
-                           num_reqs=len(lens), num_decodes=D, tile_lists={16: (tl, len(tiles))}, token_req=token_req)
+                           num_reqs=len(lens), num_decodes=D, tile_lists=lists, token_req=token_req, max_context_len=max(contexts),
+                           workspace=lambda name, shape, dtype: torch.empty(shape, dtype=dtype, device=DEV))
 
 
 def g(seed):
@@ -191,7 +194,7 @@ def _plain_rows_attention(qa, qr, rows, C, scale, sink, pos):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H, C, R, page", [(3, 40, 8, 16), (20, 16, 4, 8), (4, 136, 8, 32)])
+@pytest.mark.parametrize("H, C, R, page", [(3, 40, 8, 16), (20, 16, 4, 8), (4, 136, 8, 32), (9, 64, 32, 16), (70, 24, 8, 16)])
 def test_latent_attention_sees_exactly_the_keys_up_to_its_own(H, C, R, page, dtype):
     """One key stands out (it is the query's own direction, scaled), at places where a fault would show: the first token,
     a far key, the last row of a page and the first of the next, the query's own key, and the key just after the query
