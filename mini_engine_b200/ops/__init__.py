@@ -25,7 +25,7 @@ _PROTOS = {
     "me_hc_norm": [_P, _L, _I, _P, _I, _P, _P, _P, _P, _F, _P, _I, _P, _I, _I, _P],
     "me_short_conv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_polynorm": [_P, _I, _L, _P, _F, _P, _I, _L, _I, _I, _P],
-    "me_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "me_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "me_mlstm_out": [_P, _P, _L, _I, _P, _F, _P, _I, _I, _I, _I, _P],
     "me_latent_prep": [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "me_latent_attention": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
@@ -1038,11 +1038,15 @@ def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor)
 
 
 # ---- the matrix-memory recurrence ------------------------------------------------------------------
+mlstm_chunks = True       # portions of prompts by chunks of tokens (False: token by token, always); a switch for comparisons
+
+
 def mlstm_scan(proj: torch.Tensor, offsets: dict, bias_i: torch.Tensor, bias_f: torch.Tensor, gate_cap: float,
                S: torch.Tensor, n: torch.Tensor, m: torch.Tensor, meta, state_slots: torch.Tensor, o: torch.Tensor,
                num_heads: int, dim: int, vdim: int, q_scale: float) -> None:
     """Walks every request's tokens of this step through the recurrence from the state in its slot (see csrc/mlstm.cu).
-    ``proj`` [T, N] float32 holds q, k, v, i, f at the column ``offsets``; ``o`` [T, heads * vdim] float32."""
+    ``proj`` [T, N] float32 holds q, k, v, i, f at the column ``offsets``; ``o`` [T, heads * vdim] float32.  A step in
+    which some request brings several tokens runs the kernel that takes a chunk of 64 tokens at a time (``mlstm_chunks``)."""
     T = proj.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "mlstm_scan: projections must be float32 rows")
     _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (S, n, m, o, bias_i, bias_f)), "mlstm_scan: float32 state")
@@ -1052,7 +1056,7 @@ def mlstm_scan(proj: torch.Tensor, offsets: dict, bias_i: torch.Tensor, bias_f: 
     _call("me_mlstm_scan", proj.data_ptr(), proj.stride(0), offsets["q"], offsets["k"], offsets["v"], offsets["i"], offsets["f"],
           bias_i.data_ptr(), bias_f.data_ptr(), float(gate_cap), S.data_ptr(), n.data_ptr(), m.data_ptr(),
           meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), state_slots.data_ptr(), o.data_ptr(), meta.num_reqs,
-          num_heads, dim, vdim, float(q_scale), _stream())
+          num_heads, dim, vdim, float(q_scale), 1 if (mlstm_chunks and T > meta.num_reqs) else 0, _stream())
 
 
 def mlstm_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
