@@ -61,8 +61,10 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3, mi = lane >> 3;
   const int tq = LM_ROWS / gp;
-  const int b = PARTIAL ? blockIdx.x : tiles[2 * blockIdx.x];
-  const int q0 = PARTIAL ? 0 : tiles[2 * blockIdx.x + 1];
+  // (the list's last tiles of a request see the most keys: they start first)
+  const int tile = PARTIAL ? 0 : (int)(gridDim.x - 1 - blockIdx.x);
+  const int b = PARTIAL ? blockIdx.x : tiles[2 * tile];
+  const int q0 = PARTIAL ? 0 : tiles[2 * tile + 1];
   const int h0 = blockIdx.y * gp;
   const int chunk = blockIdx.z % chunks, split = blockIdx.z / chunks, splits = gridDim.z / chunks;
   const int c0 = chunk * LM_CCHUNK, ccols = min(LM_CCHUNK, C - c0);

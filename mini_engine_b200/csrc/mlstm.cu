@@ -9,12 +9,12 @@
 //   gi = cap tanh((x_i + b_i) / cap),   gf = logsigmoid(cap tanh((x_f + b_f) / cap)).
 // The scan kernel walks a request's tokens of this step in order from the state its slot holds (from zero when the
 // portion starts at position 0) and leaves the new state there; everything is float32, and a token's result does
-// not depend on where the sequence was cut.  One block = one request x one head x MLSTM_VB columns of S; the
+// not depend on where the sequence was cut.  One block = one request x one head x MLSTM_VB (16) columns of S; the
 // blocks of a head each keep n and m (the first one stores them).  A second kernel divides each head's o by its
 // root mean square and applies the weight and the output gate.
 #include "common.cuh"
 
-constexpr int MLSTM_VB = 32, MLSTM_DY = 8, MLSTM_THREADS = MLSTM_VB * MLSTM_DY;
+constexpr int MLSTM_VB = 16, MLSTM_DY = 16, MLSTM_THREADS = MLSTM_VB * MLSTM_DY;
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -321,16 +321,17 @@ ME_API int me_mlstm_scan(const float* proj, int64_t ld, int off_q, int off_k, in
       attr_set = true;
     }
   }
-  if (chunked && D <= 128) {
+  if (chunked && D <= 256) {
     // portions of prompts: a chunk of tokens at a time
     const size_t csmem = sizeof(float) * ((size_t)D * (MLSTM_VB + 1) + D + 2 * (size_t)MLSTM_LC * (D + 1) + MLSTM_LC * (MLSTM_VB + 1) +
                                           MLSTM_LC * (MLSTM_LC + 1) + 5 * MLSTM_LC);
-    auto kernel = D <= 64 ? mlstm_chunk_kernel<64> : mlstm_chunk_kernel<128>;
-    static bool cattr_set[2] = {false, false};
-    if (!cattr_set[D <= 64 ? 0 : 1]) {
+    const int form = D <= 64 ? 0 : (D <= 128 ? 1 : 2);
+    auto kernel = form == 0 ? mlstm_chunk_kernel<64> : (form == 1 ? mlstm_chunk_kernel<128> : mlstm_chunk_kernel<256>);
+    static bool cattr_set[3] = {false, false, false};
+    if (!cattr_set[form]) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
       ME_REQUIRE(e == cudaSuccess, "me_mlstm_scan: cannot raise shared memory: %s", cudaGetErrorString(e));
-      cattr_set[D <= 64 ? 0 : 1] = true;
+      cattr_set[form] = true;
     }
     me_launch(kernel, dim3(B, H, (V + MLSTM_VB - 1) / MLSTM_VB), dim3(MLSTM_THREADS), csmem, stream, proj, ld, off_q, off_k, off_v,
               off_i, off_f, bias_i, bias_f, cap, S_state, n_state, m_state, cu_seqlens, context_lens, state_slots, o, H, D, V,

@@ -22,7 +22,7 @@ MAX_HEAD_DIM = 256
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 _PROTOS = {
     "me_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _I, _F, _I, _L, _P],
-    "me_hc_norm": [_P, _L, _I, _P, _I, _P, _P, _P, _P, _F, _P, _I, _P, _I, _I, _P],
+    "me_hc_norm": [_P, _L, _I, _P, _I, _P, _P, _P, _P, _F, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _P],
     "me_short_conv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_polynorm": [_P, _I, _L, _P, _F, _P, _I, _L, _I, _I, _P],
     "me_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
@@ -989,11 +989,13 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor
 # ---- several residual streams, layer norm, short convolutions, PolyNorm ----------------------------
 def hc_norm(streams: torch.Tensor, *, update=None, mix_in: Optional[torch.Tensor] = None,
             norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, out: Optional[torch.Tensor] = None,
-            rows: Optional[torch.Tensor] = None) -> None:
+            rows: Optional[torch.Tensor] = None, conv=None) -> None:
     """One pass over the residual streams ``streams`` [S, T, W] (float32): apply the pending ``update`` = (y [T, W],
     mix [S, S] indexed [from, to], out weights [S]): x_r <- sum_s mix[s, r] x_s + out[r] y; then, with ``norm_weight``,
     write the layer norm of u = sum_s mix_in[s] x_s (every stream once without ``mix_in``) to ``out``.  With ``rows``
-    only those tokens are read and the streams stay as they are."""
+    only those tokens are read and the streams stay as they are.  ``conv`` = (weight [W, taps], state [slots, taps-1, W] or
+    None, state slots, context lengths), for steps in which every request brings one token (token t is request t): the
+    output is then h + conv(h) as ``short_conv`` computes it, and the state moves on, in the same kernel."""
     _need(streams.dim() == 3 and streams.dtype == torch.float32 and streams.is_contiguous(), "hc_norm: streams must be float32 [S, T, W]")
     S, T, W = streams.shape
     y = mix = outw = None
@@ -1008,8 +1010,18 @@ def hc_norm(streams: torch.Tensor, *, update=None, mix_in: Optional[torch.Tensor
         _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == W, "hc_norm: norm weight must be float32 [W]")
         _need(out is not None and out.is_contiguous() and tuple(out.shape) == (n, W), "hc_norm: output shape")
     _need(rows is None or rows.dtype == torch.int32, "hc_norm: rows must be int32")
+    cw = cs = slots = lens = None
+    taps = 0
+    if conv is not None:
+        cw, cs, slots, lens = conv
+        taps = cw.shape[1]
+        _need(rows is None and norm_weight is not None and cw.dtype == torch.float32 and cw.is_contiguous() and cw.shape[0] == W
+              and slots.numel() == T and lens.numel() == T, "hc_norm: the convolution needs a request per token")
+        _need(taps == 1 or (cs is not None and cs.dtype == torch.float32 and cs.is_contiguous()
+                            and tuple(cs.shape[1:]) == (taps - 1, W)), "hc_norm: the convolution's state")
     _call("me_hc_norm", streams.data_ptr(), T * W, S, _ptr(y), _dt(y) if y is not None else 0, _ptr(mix), _ptr(outw), _ptr(mix_in),
-          _ptr(norm_weight), float(eps), _ptr(out), _dt(out) if out is not None else 0, _ptr(rows), n, W, _stream())
+          _ptr(norm_weight), float(eps), _ptr(out), _dt(out) if out is not None else 0, _ptr(rows), n, W, _ptr(cw),
+          _ptr(cs) if taps > 1 else 0, _ptr(slots), _ptr(lens), taps, _stream())
 
 
 def short_conv(h: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], token_req: torch.Tensor, meta,

@@ -159,15 +159,25 @@ class HyperConnectionBlock(Block):
 
     def forward(self, residual, delta, ctx, call, upcoming=None):
         """``residual`` [streams, T, width]; ``delta``: the ``StreamUpdate`` the block before left (or None)."""
-        import torch
-        h = self.mixer_norm.forward(residual, delta, ctx, mix_in=self.p("hc1.in"), out_dtype=torch.float32, out_name="norm_h")
-        y = self.mixer.forward(self.conv1.forward(h, ctx, call.cache_slot), ctx, call)
+        y = self.mixer.forward(self._normed(self.mixer_norm, self.conv1, "hc1.in", residual, delta, ctx, call), ctx, call)
         update = StreamUpdate(y, self.p("hc1.mix"), self.p("hc1.out"))
         if self.feed_forward is None:
             return update
-        h = self.feed_forward_norm.forward(residual, update, ctx, mix_in=self.p("hc2.in"), out_dtype=torch.float32, out_name="norm_h")
-        y = self.feed_forward.forward(self.conv2.forward(h, ctx, call.cache_slot), ctx)
+        y = self.feed_forward.forward(self._normed(self.feed_forward_norm, self.conv2, "hc2.in", residual, update, ctx, call), ctx)
         return StreamUpdate(y, self.p("hc2.mix"), self.p("hc2.out"))
+
+    def _normed(self, norm, conv, mix_in, residual, delta, ctx, call):
+        """What a sub-layer reads: the pending update, the mix of the streams, the norm and h + conv(h).  In a step where
+        every request brings one token the convolution needs no neighbour and runs inside the norm's kernel."""
+        import torch
+        meta = ctx.attn_meta
+        if self.fuse_decode_conv and meta.num_decodes == meta.num_reqs and conv.residual and hasattr(norm, "param"):
+            state = ctx.state(call.cache_slot, conv.state_name) if conv.taps > 1 else None
+            return norm.forward(residual, delta, ctx, mix_in=self.p(mix_in), out_name="conv_out", conv=(conv.p(conv.param), state))
+        h = norm.forward(residual, delta, ctx, mix_in=self.p(mix_in), out_dtype=torch.float32, out_name="norm_h")
+        return conv.forward(h, ctx, call.cache_slot)
+
+    fuse_decode_conv = True      # a switch for comparisons
 
 
 @dataclass(frozen=True)

@@ -64,7 +64,10 @@ class LayerNorm(Norm):
         return [ParamDecl(self.param, (self.size,), init="norm", role="vector")]
 
     def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False, *,
-                mix_in: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, out_name: str = "norm_out"):
+                mix_in: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, out_name: str = "norm_out",
+                conv=None):
+        """``conv`` = (weight, state or None): in a step where every request brings one token, the short convolution that
+        follows the norm (h + conv(h), its state moved on) runs in the norm's kernel; the result is then that sum."""
         streams = residual if residual.dim() == 3 else residual.unsqueeze(0)
         update = None
         if isinstance(delta, StreamUpdate):
@@ -79,7 +82,10 @@ class LayerNorm(Norm):
             update = (delta, self._ones, self._ones.view(1))
         n = streams.shape[1] if rows is None else rows.shape[0]
         out = ctx.buffer(out_name, (n, self.size), out_dtype or ctx.act_dtype)
-        ops.hc_norm(streams, update=update, mix_in=mix_in, norm_weight=self.p(self.param), eps=self.eps, out=out, rows=rows)
+        if conv is not None:
+            conv = (*conv, ctx.state_slots, ctx.attn_meta.context_lens)
+        ops.hc_norm(streams, update=update, mix_in=mix_in, norm_weight=self.p(self.param), eps=self.eps, out=out, rows=rows,
+                    conv=conv)
         return out
 
 

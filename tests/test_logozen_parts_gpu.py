@@ -106,6 +106,30 @@ def test_short_convolution_in_portions_with_slots_used_again(taps):
     assert torch.allclose(torch.cat(got[1]).double(), ref[1][:pos[1]], atol=1e-5)
 
 
+@pytest.mark.parametrize("taps", [1, 2, 4])
+def test_norm_and_convolution_in_one_kernel_for_single_tokens(taps):
+    """Two requests token by token (the second starts later, in a slot that holds another request's leftovers): layer norm of
+    the mixed streams, then h + conv(h) with the state moved on, against the plain functions on the whole sequences."""
+    ops = _ops()
+    S, W, eps, n = 3, 50, 1e-5, 9
+    xs = [torch.randn(S, n, W, generator=g(20 + r)) * 2 for r in range(2)]
+    inw, nw = torch.rand(S, generator=g(1)) + 0.2, torch.rand(W, generator=g(2)) + 0.5
+    wt = torch.randn(W, taps, generator=g(3)) * 0.5
+    ref = [plain.causal_conv_residual(plain.layer_norm(torch.einsum("s,stw->tw", inw.double(), x.double()), nw.double(), eps), wt.double())
+           for x in xs]
+    state = torch.full((4, max(taps - 1, 1), W), float("nan"), device=DEV)[:, :taps - 1].contiguous()
+    slots = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    for t in range(n + 2):
+        live = [r for r in range(2) if 0 <= t - 2 * r < n]               # request 1 starts two steps later
+        x = torch.stack([xs[r][:, t - 2 * r] for r in live], dim=1).contiguous().to(DEV)          # [S, live, W]
+        out = torch.empty(len(live), W, device=DEV)
+        lens = torch.tensor([t - 2 * r + 1 for r in live], dtype=torch.int32, device=DEV)
+        ops.hc_norm(x, mix_in=inw.to(DEV), norm_weight=nw.to(DEV), eps=eps, out=out,
+                    conv=(wt.to(DEV), state if taps > 1 else None, slots[live].contiguous(), lens))
+        for k, r in enumerate(live):
+            assert torch.allclose(out[k].cpu().double(), ref[r][t - 2 * r], atol=2e-5), f"request {r} token {t - 2 * r}"
+
+
 # ---- PolyNorm ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("F", [24, 333, 2048])
 def test_polynorm(F):
@@ -278,6 +302,30 @@ def test_latent_prep_norms_rotates_and_writes_the_cache(rot_dims):
             assert torch.allclose(pool[slots[t]].cpu().double(), torch.cat((c[t], kr[t])), atol=3e-6)
     assert float(pool[[1, 3, 5, 6, 8]].abs().max()) == 0.0
     assert torch.allclose(gate.cpu().double(), torch.sigmoid(p64[:, offs["g"]:]), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [1, 7, 16, 40])
+def test_per_head_products_and_rows(T, dtype):
+    """Both up-projections in their layouts: q [T, H, D] against W_uk [H, D, C]; latents [H, T, C] against the transposed
+    view of W_uv [H, V, C], then heads into rows [T, H * V]."""
+    ops = _ops()
+    H, D, C, V = 5, 24, 40, 12
+    q = torch.randn(T, H, D, generator=g(T)).to(dtype).to(DEV)
+    uk = torch.randn(H, D, C, generator=g(1)).to(dtype).to(DEV)
+    out = torch.empty(H, T, C, dtype=dtype, device=DEV)
+    ops.batched_heads_mm(q.transpose(0, 1), uk, out)
+    ref = torch.einsum("thd,hdc->htc", q.double(), uk.double())
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert torch.allclose(out.double(), ref, atol=tol * 10, rtol=tol)
+    lat = torch.randn(H, T, C, generator=g(2)).to(dtype).to(DEV)
+    uv = torch.randn(H, V, C, generator=g(3)).to(dtype).to(DEV)
+    ref = torch.einsum("htc,hvc->thv", lat.double(), uv.double()).reshape(T, H * V)
+    heads = torch.empty(H, T, V, dtype=dtype, device=DEV)
+    ops.batched_heads_mm(lat, uv.transpose(1, 2), heads)
+    rows = torch.empty(T, H * V, dtype=dtype, device=DEV)
+    ops.heads_to_rows(heads, rows)
+    assert torch.allclose(rows.double(), ref, atol=tol * 10, rtol=tol)
 
 
 def test_embedding_is_scaled_and_starts_every_stream():
