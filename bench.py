@@ -657,7 +657,7 @@ def _logozen_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
     """What the design's own kernels have to move or do in a prefill step of T tokens, and the fraction of the measured
     peak that their summed time makes: bytes for the element-wise kernels, multiply-adds for attention and recurrence."""
     W, S = cfg["width"], cfg["streams"]
-    need = {"me_hc_norm": 0.0, "me_short_conv": 0.0, "me_polynorm": 0.0, "me_latent_attention": 0.0, "me_mlstm_scan": 0.0}
+    need = {"me_hc_norm": 0.0, "me_short_conv": 0.0, "me_polynorm": 0.0, "me_latent_attention_mma": 0.0, "me_mlstm_scan": 0.0}
     for layer in cfg["layers"]:
         m = layer["mixer"]
         subs = 2 if layer["mlp"] is not None else 1
@@ -666,7 +666,7 @@ def _logozen_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
         if layer["mlp"] is not None:
             need["me_polynorm"] += T * layer["mlp"]["ff"] * (4 + item)
         if layer["type"] == "latent_attention":
-            need["me_latent_attention"] += 2.0 * m["heads"] * (2 * m["kv_rank"] + m["rot_dim"]) * T * (T + 1) / 2
+            need["me_latent_attention_mma"] += 2.0 * m["heads"] * (2 * m["kv_rank"] + m["rot_dim"]) * T * (T + 1) / 2
         else:
             need["me_mlstm_scan"] += 4.0 * m["heads"] * m["dim"] * m["vdim"] * T
     need["me_hc_norm"] += W * (4 * S + item)                               # the last norm, one row
@@ -675,7 +675,7 @@ def _logozen_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
         us = times.get(name, {}).get("us")
         if not us or not amount:
             continue
-        flops = name in ("me_latent_attention", "me_mlstm_scan")
+        flops = name in ("me_latent_attention_mma", "me_mlstm_scan")
         rate = amount / (us * 1e-6)
         out[name] = {"us": us, ("flops" if flops else "bytes"): amount,
                      "frac": round(rate / (pk["bf16_tflops"] * 1e12 if flops else pk["hbm_gbs"] * 1e9), 4),
@@ -697,7 +697,7 @@ def run_logozen_mode(args) -> int:
         for label, c in (("logozen", cfg), ("qwen3", twin)):
             model = Model.of_config(c, f"{label} {size}", args.seed)
             top = max(batches)
-            llm = make_engine(model, args, max_seqs=max(top, 4), budget=max(T, top), context=T + 256,
+            llm = make_engine(model, args, max_seqs=top + 2, budget=max(T, top), context=T + 256,   # (a state slot each, and the prompt's)
                               pages=(top + 2) * ((T + 128) // args.page_size + 2), enable_prefix_caching=False)
             runner, cache = llm.model_runner, llm.cache
             prompts = random_prompts(top, T // 2, model.vocab, args.seed + 1)

@@ -7,7 +7,7 @@
 // once for gp heads.  Four warps, each a strip of 16 rows; S = Q K^T with Q and K fragments from shared memory by
 // ldmatrix, P rounded to bfloat16 in registers, O += P V with V fragments by transposing ldmatrix from the same tile;
 // key tiles of 64 arrive by cp.async in two buffers, rows padded to a multiple of 64 values and their 16-byte pieces
-// XOR-swizzled.  A block accumulates at most 128 of the C output columns (grid.z takes the others and repeats S).
+// XOR-swizzled.  A block accumulates at most 256 of the C output columns (grid.z takes the others and repeats S).
 // Key tiles start at multiples of 64 from position 0.
 //
 // Portions of prompts: blocks by the step's query-tile list; the softmax's sink and the gate are applied at the end.
@@ -20,7 +20,7 @@ namespace {
 
 using namespace mma_prims;
 
-constexpr int LM_ROWS = 64, LM_KEYS = 64, LM_THREADS = 128, LM_CCHUNK = 128;
+constexpr int LM_ROWS = 64, LM_KEYS = 64, LM_THREADS = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 
 // 16-byte piece ``piece`` of row ``row`` in a tile whose rows hold ``ldp`` pieces (a multiple of 8)
@@ -44,7 +44,8 @@ __device__ __forceinline__ void load_key_tile(bf16* ks, const bf16* __restrict__
   }
 }
 
-template <bool PARTIAL>
+// LM_CCHUNK: output columns a block accumulates (128, or 256 for latents beyond 128: twice the registers, S computed once)
+template <bool PARTIAL, int LM_CCHUNK>
 __global__ void __launch_bounds__(LM_THREADS)
 latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ q_rot, const bf16* __restrict__ pool,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_seqlens,
@@ -287,16 +288,17 @@ ME_API int me_latent_attention_mma(const void* q_abs, const void* q_rot, const v
                                    int R, int page_size, float scale, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   ME_REQUIRE(me_latent_attention_mma_takes(C, R), "me_latent_attention_mma: rows of %d + %d values are not taken", C, R);
-  const int gp = me_latent_attention_mma_heads_per_block(H), chunks = (C + LM_CCHUNK - 1) / LM_CCHUNK;
+  const int gp = me_latent_attention_mma_heads_per_block(H), cc = C > 128 ? 256 : 128, chunks = (C + cc - 1) / cc;
   const size_t smem = lm_smem(C, R);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  auto kernel = cc == 256 ? latent_attn_mma_kernel<false, 256> : latent_attn_mma_kernel<false, 128>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[cc == 256]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     ME_REQUIRE(e == cudaSuccess, "me_latent_attention_mma: cannot raise shared memory: %s", cudaGetErrorString(e));
-    attr_set = true;
+    attr_set[cc == 256] = true;
   }
   ME_REQUIRE((H + gp - 1) / gp <= 65535, "me_latent_attention_mma: too many heads");
-  me_launch(latent_attn_mma_kernel<false>, dim3(num_tiles, (H + gp - 1) / gp, chunks), dim3(LM_THREADS), smem, stream,
+  me_launch(kernel, dim3(num_tiles, (H + gp - 1) / gp, chunks), dim3(LM_THREADS), smem, stream,
             (const bf16*)q_abs, (const bf16*)q_rot, (const bf16*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles,
             sink, gate, (bf16*)out, (float*)nullptr, T_total, H, C, R, page_size, scale * LOG2E, gp, chunks, 0);
   ME_LAUNCH_CHECK("me_latent_attention_mma");
@@ -314,16 +316,16 @@ ME_API int me_latent_attention_decode(const void* q_abs, const void* q_rot, cons
   ME_REQUIRE(me_latent_attention_mma_takes(C, R), "me_latent_attention_decode: rows of %d + %d values are not taken", C, R);
   ME_REQUIRE(splits >= 1 && keys_per_split > 0 && keys_per_split % LM_KEYS == 0 && partial != nullptr,
              "me_latent_attention_decode: %d ranges of %d keys", splits, keys_per_split);
-  const int chunks = (C + LM_CCHUNK - 1) / LM_CCHUNK;
+  const int chunks = (C + 127) / 128;
   ME_REQUIRE(chunks * splits <= 65535 && H <= 65535, "me_latent_attention_decode: too many blocks");
   const size_t smem = lm_smem(C, R);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     ME_REQUIRE(e == cudaSuccess, "me_latent_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  me_launch(latent_attn_mma_kernel<true>, dim3(num_decodes, (H + LM_ROWS - 1) / LM_ROWS, chunks * splits), dim3(LM_THREADS), smem,
+  me_launch(latent_attn_mma_kernel<true, 128>, dim3(num_decodes, (H + LM_ROWS - 1) / LM_ROWS, chunks * splits), dim3(LM_THREADS), smem,
             stream, (const bf16*)q_abs, (const bf16*)q_rot, (const bf16*)pool, block_tables, bt_stride, cu_seqlens, context_lens,
             (const int*)nullptr, (const float*)nullptr, (const float*)nullptr, (bf16*)nullptr, partial, T_total, H, C, R, page_size,
             scale * LOG2E, LM_ROWS, chunks, keys_per_split);
