@@ -254,8 +254,8 @@ class LogozenConfig(ModelConfig):
         for name in ("vocab_size", "hidden_size", "streams", "canon_taps"):
             if getattr(cfg, name) < 1:
                 raise ConfigError(f"{name} must be positive, got {getattr(cfg, name)}")
-        if cfg.streams > 8:
-            raise ConfigError(f"{cfg.streams} residual streams are not supported (up to 8)")
+        if cfg.streams > 16:
+            raise ConfigError(f"{cfg.streams} residual streams are not supported (up to 16)")
         if not cfg.norm_eps > 0:
             raise ConfigError("norm.eps must be positive")
         return cfg

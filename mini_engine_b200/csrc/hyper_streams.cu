@@ -9,7 +9,7 @@
 // ``in`` every stream counts once (the sum of the streams).  Streams, sums and statistics are float32.
 #include "common.cuh"
 
-constexpr int HC_MAX_STREAMS = 8;
+constexpr int HC_MAX_STREAMS = 16;
 
 // NS: the number of streams the loops are unrolled for (S <= NS)
 template <typename TY, typename TO, int NS>
@@ -23,10 +23,10 @@ hc_norm_kernel(float* __restrict__ x, int64_t stream_stride, int S, const TY* __
   __shared__ float red[32];
   __shared__ float c_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], c_out[HC_MAX_STREAMS], c_in[HC_MAX_STREAMS];
   const int tid = threadIdx.x;
-  if (tid < S * S) c_mix[tid] = mix ? mix[tid] : 0.f;
-  if (tid < S) {
-    c_out[tid] = outw ? outw[tid] : 0.f;
-    c_in[tid] = inw ? inw[tid] : 1.f;
+  for (int i = tid; i < S * S; i += blockDim.x) c_mix[i] = mix ? mix[i] : 0.f;
+  for (int i = tid; i < S; i += blockDim.x) {
+    c_out[i] = outw ? outw[i] : 0.f;
+    c_in[i] = inw ? inw[i] : 1.f;
   }
   pdl_wait();
   pdl_launch_dependents();
@@ -143,6 +143,7 @@ ME_API int me_hc_norm(float* x, int64_t stream_stride, int S, const void* y, int
     if (S == 1) rc = launch_hc_norm<TY, TO, 1>(x, stream_stride, S, y, mix, outw, inw, normw, eps, out, rows, n, W, threads, smem, conv_w, conv_state, state_slots, context_lens, taps, stream);
     else if (S == 2) rc = launch_hc_norm<TY, TO, 2>(x, stream_stride, S, y, mix, outw, inw, normw, eps, out, rows, n, W, threads, smem, conv_w, conv_state, state_slots, context_lens, taps, stream);
     else if (S <= 4) rc = launch_hc_norm<TY, TO, 4>(x, stream_stride, S, y, mix, outw, inw, normw, eps, out, rows, n, W, threads, smem, conv_w, conv_state, state_slots, context_lens, taps, stream);
+    else if (S <= 8) rc = launch_hc_norm<TY, TO, 8>(x, stream_stride, S, y, mix, outw, inw, normw, eps, out, rows, n, W, threads, smem, conv_w, conv_state, state_slots, context_lens, taps, stream);
     else rc = launch_hc_norm<TY, TO, HC_MAX_STREAMS>(x, stream_stride, S, y, mix, outw, inw, normw, eps, out, rows, n, W, threads, smem, conv_w, conv_state, state_slots, context_lens, taps, stream);
   }));
   if (rc) return rc;

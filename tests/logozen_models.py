@@ -54,7 +54,11 @@ R = config(64, 40, 5, 2, [mlstm(3, 16, 32, gate_cap=10.0, ff=56), mlstm(1, 40, 7
 # S: attention alone, eight streams, three taps, a latent wider than 128 (the kernel's second form)
 S = config(80, 56, 8, 3, [latent(4, 24, 8, 16, 136, ff=64), latent(4, 24, 8, 16, 136, ff=None)], eps=1e-5, embed_scale=2.5)
 
-ALL = {"P": (P, 1, 16), "Q": (Q, 2, 8), "R": (R, 3, 16), "S": (S, 4, 32)}        # config, seed, page size
+# U: no size a multiple of 8 (width, feed-forward, heads' sizes, latent), eleven streams, seven taps, six rotated of ten dims
+U = config(75, 52, 11, 7, [mlstm(5, 12, 20, gate_cap=30.0, ff=70), latent(5, 10, 10, 12, 20, rot_dims=6, base=300.0, ff=70),
+                            latent(7, 6, 2, 9, 13, base=50.0, ff=None)], eps=2e-5, embed_scale=5.0)
+
+ALL = {"P": (P, 1, 16), "Q": (Q, 2, 8), "R": (R, 3, 16), "S": (S, 4, 32), "U": (U, 5, 16)}        # config, seed, page size
 
 
 def tensors(cfg: dict, seed: int, gain: float = 1.2) -> dict[str, torch.Tensor]:

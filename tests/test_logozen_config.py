@@ -59,7 +59,7 @@ def test_config_is_found_by_its_architecture_key(tmp_path):
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=3), "rot.dims"),
     (lambda c: c["layers"][1]["mixer"].update(gate_cap=0.0), "gate_cap"),
     (lambda c: c.pop("norm"), "norm"),
-    (lambda c: c.update(streams=9), "streams"),
+    (lambda c: c.update(streams=17), "streams"),
     (lambda c: c["canon"].update(taps=0), "canon_taps"),
 ])
 def test_what_the_engine_cannot_honour_is_refused(change, text):

@@ -9,7 +9,7 @@ import plain_logozen
 
 pytestmark = pytest.mark.gpu
 LENGTHS = {"P": (70, 45, 100, 33, 64, 129), "Q": (37, 88, 50, 112, 41, 65), "R": (90, 47, 130, 36, 80, 52),
-           "S": (150, 33, 97, 64, 200, 41)}
+           "S": (150, 33, 97, 64, 200, 41), "U": (61, 30, 99, 17, 70, 44)}
 # Centred difference of a position's logits, root mean square over the vocabulary, relative to that of the logits: the
 # worst position, and the mean over a request's positions.  bfloat16 rounds activations to 8 bits between the parts,
 # which costs these narrow models a few per cent at some positions; a wrong key, state or sink costs tens of per cent.
@@ -60,7 +60,7 @@ def _check(name, dtype, reqs, got, tag):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
 def test_each_request_alone_and_whole(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_whole(reqs))
@@ -68,7 +68,7 @@ def test_each_request_alone_and_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
 def test_prompt_then_token_by_token(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_decode_tail(reqs, tail=40))
@@ -76,7 +76,7 @@ def test_prompt_then_token_by_token(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
 def test_portions_of_changing_size(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_portions(reqs))
@@ -86,7 +86,7 @@ def test_portions_of_changing_size(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "U"])
 def test_mixed_batches_with_pages_and_slots_used_again(name, dtype):
     reqs = _requests(name) + _requests(name)[:4]
     steps = helpers.trace_mixed(reqs, max_live=4, seed=3)
