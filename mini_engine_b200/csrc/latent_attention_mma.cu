@@ -15,12 +15,13 @@
 // and latent_merge_kernel joins the ranges, adds the sink to the denominator and applies the gate.
 #include "common.cuh"
 #include "mma_prims.cuh"
+#include <algorithm>
 
 namespace {
 
 using namespace mma_prims;
 
-constexpr int LM_ROWS = 64, LM_KEYS = 64, LM_THREADS = 128;
+constexpr int LM_ROWS = 64, LM_THREADS = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 
 // 16-byte piece ``piece`` of row ``row`` in a tile whose rows hold ``ldp`` pieces (a multiple of 8)
@@ -28,6 +29,7 @@ __device__ __forceinline__ bf16* tptr(bf16* base, int row, int piece, int ldp) {
   return base + ((row * ldp + (piece ^ (row & 7))) << 3);
 }
 
+template <int LM_KEYS>
 __device__ __forceinline__ void load_key_tile(bf16* ks, const bf16* __restrict__ pool, const int* __restrict__ bt,
                                               int page_size, int dk, int pieces, int ldp, int kt, int k_end) {
   for (int c = threadIdx.x; c < LM_KEYS * ldp; c += LM_THREADS) {
@@ -44,15 +46,16 @@ __device__ __forceinline__ void load_key_tile(bf16* ks, const bf16* __restrict__
   }
 }
 
-// LM_CCHUNK: output columns a block accumulates (128, or 256 for latents beyond 128: twice the registers, S computed once)
-template <bool PARTIAL, int LM_CCHUNK>
+// LM_CCHUNK: output columns a block accumulates (128, or 256 for latents beyond 128: twice the registers, S computed once).
+// LM_KEYS: keys a tile (64, or 32 where only that lets two blocks share an SM).
+template <bool PARTIAL, int LM_CCHUNK, int LM_KEYS>
 __global__ void __launch_bounds__(LM_THREADS)
 latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ q_rot, const bf16* __restrict__ pool,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ context_lens, const int* __restrict__ tiles,
                        const float* __restrict__ sink, const float* __restrict__ gate, bf16* __restrict__ out,
                        float* __restrict__ partial, int T_total, int H, int C, int R, int page_size, float scale_log2,
-                       int gp, int chunks, int keys_per_split) {
+                       int gp, int chunks, int keys_per_split, int nbuf) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   pdl_wait();
   pdl_launch_dependents();
@@ -103,15 +106,15 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
       }
       cp_async16(tptr(qs, row, piece, ldp), src, ok);
     }
-    load_key_tile(kbuf, pool, bt, page_size, dk, pieces, ldp, k_begin, k_end);
+    load_key_tile<LM_KEYS>(kbuf, pool, bt, page_size, dk, pieces, ldp, k_begin, k_end);
     cp_async_commit();
   }
 
   for (int it = 0; it < n_tiles; ++it) {
     const int kt = k_begin + it * LM_KEYS;
-    bf16* ks = kbuf + (it & 1) * LM_KEYS * ldp * 8;
-    if (it + 1 < n_tiles) {
-      load_key_tile(kbuf + ((it + 1) & 1) * LM_KEYS * ldp * 8, pool, bt, page_size, dk, pieces, ldp, kt + LM_KEYS, k_end);
+    bf16* ks = kbuf + (nbuf == 2 ? (it & 1) : 0) * LM_KEYS * ldp * 8;
+    if (nbuf == 2 && it + 1 < n_tiles) {
+      load_key_tile<LM_KEYS>(kbuf + ((it + 1) & 1) * LM_KEYS * ldp * 8, pool, bt, page_size, dk, pieces, ldp, kt + LM_KEYS, k_end);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -194,6 +197,10 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
       }
     }
     __syncthreads();
+    if (nbuf == 1 && it + 1 < n_tiles) {        // one buffer: the next tile comes once this one is done with; a second block
+      load_key_tile<LM_KEYS>(kbuf, pool, bt, page_size, dk, pieces, ldp, kt + LM_KEYS, k_end);   // of the SM computes meanwhile
+      cp_async_commit();
+    }
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -266,9 +273,26 @@ latent_merge_kernel(const float* __restrict__ partial, const int* __restrict__ c
   }
 }
 
-size_t lm_smem(int C, int R) {
+size_t lm_smem(int C, int R, int nbuf = 2, int keys = 64) {
   const int ldp = (((C + R) / 8) + 7) & ~7;
-  return (size_t)(LM_ROWS + 2 * LM_KEYS) * ldp * 8 * sizeof(bf16);
+  return (size_t)(LM_ROWS + nbuf * keys) * ldp * 8 * sizeof(bf16);
+}
+
+// How a prompt's key tiles are held: two buffers of 64 keys, or one buffer (of 64, or of 32 keys) where only that lets
+// another block share the SM (227 KB of shared memory; registers allow three blocks of the 128-column form and two of
+// the 256-column form): the second block computes while the first waits for its next tile.
+void lm_tiling(int C, int R, int* nbuf, int* keys) {
+  const int by_regs = C > 128 ? 2 : 3;
+  const int options[3][2] = {{2, 64}, {1, 64}, {1, 32}};
+  int best = 0;
+  for (int i = 0; i < 3; ++i) {
+    const int blocks = (int)std::min<size_t>(by_regs, (227 * 1024) / lm_smem(C, R, options[i][0], options[i][1]));
+    if (blocks > best) {
+      best = blocks;
+      *nbuf = options[i][0];
+      *keys = options[i][1];
+    }
+  }
 }
 
 }  // namespace
@@ -289,18 +313,22 @@ ME_API int me_latent_attention_mma(const void* q_abs, const void* q_rot, const v
   if (num_tiles == 0) return 0;
   ME_REQUIRE(me_latent_attention_mma_takes(C, R), "me_latent_attention_mma: rows of %d + %d values are not taken", C, R);
   const int gp = me_latent_attention_mma_heads_per_block(H), cc = C > 128 ? 256 : 128, chunks = (C + cc - 1) / cc;
-  const size_t smem = lm_smem(C, R);
-  auto kernel = cc == 256 ? latent_attn_mma_kernel<false, 256> : latent_attn_mma_kernel<false, 128>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[cc == 256]) {
+  int nbuf = 2, keys = 64;
+  lm_tiling(C, R, &nbuf, &keys);
+  const size_t smem = lm_smem(C, R, nbuf, keys);
+  const int form = (cc == 256 ? 2 : 0) + (keys == 32 ? 1 : 0);
+  auto kernel = form == 0 ? latent_attn_mma_kernel<false, 128, 64> : form == 1 ? latent_attn_mma_kernel<false, 128, 32>
+              : form == 2 ? latent_attn_mma_kernel<false, 256, 64> : latent_attn_mma_kernel<false, 256, 32>;
+  static bool attr_set[4] = {false, false, false, false};
+  if (!attr_set[form]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     ME_REQUIRE(e == cudaSuccess, "me_latent_attention_mma: cannot raise shared memory: %s", cudaGetErrorString(e));
-    attr_set[cc == 256] = true;
+    attr_set[form] = true;
   }
   ME_REQUIRE((H + gp - 1) / gp <= 65535, "me_latent_attention_mma: too many heads");
   me_launch(kernel, dim3(num_tiles, (H + gp - 1) / gp, chunks), dim3(LM_THREADS), smem, stream,
             (const bf16*)q_abs, (const bf16*)q_rot, (const bf16*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles,
-            sink, gate, (bf16*)out, (float*)nullptr, T_total, H, C, R, page_size, scale * LOG2E, gp, chunks, 0);
+            sink, gate, (bf16*)out, (float*)nullptr, T_total, H, C, R, page_size, scale * LOG2E, gp, chunks, 0, nbuf);
   ME_LAUNCH_CHECK("me_latent_attention_mma");
   return 0;
 }
@@ -314,21 +342,21 @@ ME_API int me_latent_attention_decode(const void* q_abs, const void* q_rot, cons
                                       cudaStream_t stream) {
   if (num_decodes == 0) return 0;
   ME_REQUIRE(me_latent_attention_mma_takes(C, R), "me_latent_attention_decode: rows of %d + %d values are not taken", C, R);
-  ME_REQUIRE(splits >= 1 && keys_per_split > 0 && keys_per_split % LM_KEYS == 0 && partial != nullptr,
+  ME_REQUIRE(splits >= 1 && keys_per_split > 0 && keys_per_split % 64 == 0 && partial != nullptr,
              "me_latent_attention_decode: %d ranges of %d keys", splits, keys_per_split);
   const int chunks = (C + 127) / 128;
   ME_REQUIRE(chunks * splits <= 65535 && H <= 65535, "me_latent_attention_decode: too many blocks");
   const size_t smem = lm_smem(C, R);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<true, 128, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     ME_REQUIRE(e == cudaSuccess, "me_latent_attention_decode: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  me_launch(latent_attn_mma_kernel<true, 128>, dim3(num_decodes, (H + LM_ROWS - 1) / LM_ROWS, chunks * splits), dim3(LM_THREADS), smem,
+  me_launch(latent_attn_mma_kernel<true, 128, 64>, dim3(num_decodes, (H + LM_ROWS - 1) / LM_ROWS, chunks * splits), dim3(LM_THREADS), smem,
             stream, (const bf16*)q_abs, (const bf16*)q_rot, (const bf16*)pool, block_tables, bt_stride, cu_seqlens, context_lens,
             (const int*)nullptr, (const float*)nullptr, (const float*)nullptr, (bf16*)nullptr, partial, T_total, H, C, R, page_size,
-            scale * LOG2E, LM_ROWS, chunks, keys_per_split);
+            scale * LOG2E, LM_ROWS, chunks, keys_per_split, 2);
   ME_LAUNCH_CHECK("me_latent_attention_decode");
   me_launch(latent_merge_kernel, dim3(num_decodes, H), dim3(128), 0, stream, (const float*)partial, cu_seqlens, sink, gate,
             (bf16*)out, T_total, H, C, splits);

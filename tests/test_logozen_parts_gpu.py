@@ -226,7 +226,7 @@ def _plain_rows_attention(qa, qr, rows, C, scale, sink, pos):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H, C, R, page", [(3, 40, 8, 16), (20, 16, 4, 8), (4, 136, 8, 32), (9, 64, 32, 16), (70, 24, 8, 16), (3, 40, 16, 16),
-                                           (2, 264, 24, 16)])
+                                           (2, 264, 24, 16), (2, 512, 64, 16)])
 def test_latent_attention_sees_exactly_the_keys_up_to_its_own(H, C, R, page, dtype):
     """One key stands out (it is the query's own direction, scaled), at places where a fault would show: the first token,
     a far key, the last row of a page and the first of the next, the query's own key, and the key just after the query
