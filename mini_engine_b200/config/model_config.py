@@ -264,3 +264,119 @@ class LogozenConfig(ModelConfig):
         return {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "streams": self.streams,
                 "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps}, "canon": {"taps": self.canon_taps},
                 "layers": self.layers}
+
+
+def _opt_object(raw: dict, key: str, where: str):
+    v = raw.get(key)
+    if v is not None and not isinstance(v, dict):
+        raise ConfigError(f"{where}: {key!r} must be an object or absent, got {v!r}")
+    return v
+
+
+def _glu_sizes(raw: dict, where: str) -> dict[str, Any]:
+    out = {"ff": _need(raw, "ff", int)}
+    if out["ff"] < 1:
+        raise ConfigError(f"{where}: ff must be positive")
+    if raw.get("limit") is not None:
+        out["limit"] = _need(raw, "limit", float)
+        if not out["limit"] > 0:
+            raise ConfigError(f"{where}: limit must be positive")
+    return out
+
+
+@dataclass
+class PugadraConfig(ModelConfig):
+    """Pugadra: a decoder of attention layers whose sub-layers are normalised on both sides and scaled by
+    ``residual_mult`` before they join the residual stream, with a per-layer input from the token itself behind the
+    feed-forward.  config.json keys: ``vocab``, ``width``, ``norm.eps``, ``residual_mult``, ``token_side.dim`` (absent: no
+    token input) and ``layers``: a list of ``{"type": "attention", "mixer": {heads, kv_heads, dim, vdim, scale, conv (taps),
+    rot {base, dims}, mask {size}, kv_from}, "mlp": dense {ff, limit} | moe {router {experts, top}, expert {ff, limit},
+    shared {ff, limit}} | null}``.  ``conv``, ``rot``, ``mask``, ``kv_from``, ``shared`` and every ``limit`` may be absent.
+    The embedding is also the output matrix.  The design has no limit on positions; ``max_position_embeddings`` is what
+    an int32 position allows the engine."""
+
+    norm_eps: float = 0.0
+    residual_mult: float = 1.0
+    side_dim: int = 0
+    layers: list[dict[str, Any]] = field(default_factory=list)
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "PugadraConfig":
+        layers = _need(raw, "layers", list)
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("config.json key 'layers' must be a list with at least one layer")
+        checked = []
+        for i, layer in enumerate(layers):
+            where = f"layer {i}"
+            if not isinstance(layer, dict) or layer.get("type") != "attention":
+                raise ConfigError(f"{where}: 'type' must be 'attention', got {layer.get('type') if isinstance(layer, dict) else layer!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}: lacks the object 'mixer'")
+            m: dict[str, Any] = {k: _need(mixer, k, int) for k in ("heads", "kv_heads", "dim", "vdim")}
+            m["scale"] = _need(mixer, "scale", float)
+            if any(m[k] < 1 for k in ("heads", "kv_heads", "dim", "vdim")) or m["heads"] % m["kv_heads"]:
+                raise ConfigError(f"{where}: sizes must be positive and heads a multiple of kv_heads: {m}")
+            if mixer.get("conv") is not None:
+                m["conv"] = _need(mixer, "conv", int)
+                if m["conv"] < 1:
+                    raise ConfigError(f"{where}: conv must be a positive number of taps")
+            rot = _opt_object(mixer, "rot", where)
+            if rot is not None:
+                m["rot"] = {"base": _need(rot, "base", float), "dims": _need(rot, "dims", int)}
+                if m["rot"]["dims"] % 2 or not 0 <= m["rot"]["dims"] <= m["dim"] or not m["rot"]["base"] > 0:
+                    raise ConfigError(f"{where}: rot.dims must be even and at most dim, rot.base positive: {m['rot']}")
+                if m["rot"]["dims"] and m["dim"] % 2:
+                    raise ConfigError(f"{where}: a rotated head needs an even dim, got {m['dim']}")
+            mask = _opt_object(mixer, "mask", where)
+            if mask is not None and mask.get("size") is not None:
+                m["mask"] = {"size": _need(mask, "size", int)}
+                if m["mask"]["size"] < 1:
+                    raise ConfigError(f"{where}: mask.size must be positive")
+            if mixer.get("kv_from") is not None:
+                j = m["kv_from"] = _need(mixer, "kv_from", int)
+                if not 0 <= j < i or "kv_from" in checked[j]["mixer"]:
+                    raise ConfigError(f"{where}: kv_from must name an earlier layer with keys and values of its own, got {j}")
+                src = checked[j]["mixer"]
+                if any(src[k] != m[k] for k in ("kv_heads", "dim", "vdim")) or src.get("rot") != m.get("rot"):
+                    raise ConfigError(f"{where}: layer {j}'s key/value heads, sizes and rotation differ from this layer's")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind") not in ("dense", "moe"):
+                    raise ConfigError(f"{where}: 'mlp' must be null or of kind 'dense' or 'moe', got {mlp!r}")
+                if mlp["kind"] == "dense":
+                    mlp = {"kind": "dense", **_glu_sizes(mlp, where + " mlp")}
+                else:
+                    router, expert = mlp.get("router"), mlp.get("expert")
+                    if not isinstance(router, dict) or not isinstance(expert, dict):
+                        raise ConfigError(f"{where}: a moe feed-forward needs the objects 'router' and 'expert'")
+                    out = {"kind": "moe", "router": {"experts": _need(router, "experts", int), "top": _need(router, "top", int)},
+                           "expert": _glu_sizes(expert, where + " mlp.expert")}
+                    if not 1 <= out["router"]["top"] <= out["router"]["experts"]:
+                        raise ConfigError(f"{where}: router.top must lie between 1 and router.experts")
+                    shared = _opt_object(mlp, "shared", where)
+                    if shared is not None:
+                        out["shared"] = _glu_sizes(shared, where + " mlp.shared")
+                    mlp = out
+            checked.append({"type": "attention", "mixer": m, "mlp": mlp})
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json lacks the object 'norm'")
+        side = _opt_object(raw, "token_side", "config.json")
+        eos = raw.get("eos_token_id", -1)
+        cfg = cls(architecture=architecture_name(raw), vocab_size=_need(raw, "vocab", int), hidden_size=_need(raw, "width", int),
+                  num_hidden_layers=len(checked), max_position_embeddings=int(raw.get("max_position_embeddings", 1 << 30)),
+                  eos_token_id=-1 if eos is None else int(eos), norm_eps=_need(norm, "eps", float),
+                  residual_mult=float(raw.get("residual_mult", 1.0)), side_dim=_need(side, "dim", int) if side else 0, layers=checked)
+        if cfg.vocab_size < 1 or cfg.hidden_size < 1 or cfg.side_dim < 0:
+            raise ConfigError("vocab and width must be positive, token_side.dim not negative")
+        if not cfg.norm_eps > 0:
+            raise ConfigError("norm.eps must be positive")
+        return cfg
+
+    def to_json_dict(self) -> dict[str, Any]:
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "norm": {"eps": self.norm_eps},
+             "residual_mult": self.residual_mult, "layers": self.layers}
+        if self.side_dim:
+            d["token_side"] = {"dim": self.side_dim}
+        return d

@@ -1,0 +1,123 @@
+// What lies between the packed q|k|v projection and the attention kernel of a mixer whose projections pass through a
+// short causal convolution: bias, convolution over time with the last inputs of every request as state, rotation of
+// neighbouring pairs, and the write of the new keys and values into the paged cache, in one pass.
+//
+// u_t = proj_t + bias (zeros before a request's first token), y_t = sum_j w[:, j] * u_(t - taps + 1 + j), j < taps.
+// Channels are laid out q (nh x D) | k (nkv x D) | v (nkv x Dv); a mixer that takes its keys and values from another
+// layer has only q.  Of every q and k head the first ``rot`` elements are rotated, (2i, 2i+1) by the angle
+// position * inv_freq[i], formed in double precision and rounded once, to the float32 cosine and sine.  Cache rows hold
+// [key (D) | value (Dv)] per token and kv head: pool [pages][kv head][page offset][D + Dv].
+// The state [slots][taps-1][channels] (float32) holds u at the last taps-1 positions; it is read for positions before the
+// portion's first token and renewed by a second kernel.  No slot is read for positions below 0.
+#include "common.cuh"
+
+struct ConvSrc {
+  const float* proj; int64_t stride;      // [T, >= C] float32
+  const float* bias;                      // [C] or null
+  const float* state;                     // [slots, taps-1, C] or null
+  int C, taps;
+};
+
+// u of channel c at local index src (may be negative: from the state) of a portion that starts at position ``start``.
+__device__ __forceinline__ float conv_input(const ConvSrc& s, int tok0, int src, int start, int slot, int c) {
+  if (start + src < 0) return 0.f;
+  if (src >= 0) return s.proj[(int64_t)(tok0 + src) * s.stride + c] + (s.bias ? s.bias[c] : 0.f);
+  if (slot < 0) return 0.f;
+  return s.state[((int64_t)slot * (s.taps - 1) + (src + s.taps - 1)) * s.C + c];
+}
+
+__device__ __forceinline__ float conv_output(const ConvSrc& s, const float* __restrict__ wt, int tok0, int i, int start, int slot,
+                                             int c) {
+  if (!wt) return conv_input(s, tok0, i, start, slot, c);
+  float acc = 0.f;
+  for (int j = 0; j < s.taps; ++j) acc = fmaf(wt[(int64_t)c * s.taps + j], conv_input(s, tok0, i - (s.taps - 1) + j, start, slot, c), acc);
+  return acc;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __restrict__ inv_freq, int rot,
+                    const int* __restrict__ positions, const int* __restrict__ token_req, const int* __restrict__ cu_seqlens,
+                    const int* __restrict__ context_lens, const int* __restrict__ state_slots,
+                    const int* __restrict__ slot_mapping, TO* __restrict__ q_out, TO* __restrict__ pool, int nh, int nkv, int D,
+                    int Dv, int page_size) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= s.C) return;
+  const int b = token_req[t];
+  const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
+  const int start = context_lens[b] - q_len;
+  const int i = t - tok0;
+  const int slot = state_slots[b];
+  const int Cq = nh * D, Ck = nkv * D;
+  float y = conv_output(s, wt, tok0, i, start, slot, c);
+  int d = -1;                                   // index inside a rotated head, if this channel belongs to one
+  if (c < Cq + Ck) d = (c < Cq ? c : c - Cq) % D;
+  if (d >= 0 && d < rot) {
+    const float other = conv_output(s, wt, tok0, i, start, slot, c ^ 1);   // D and rot are even: the pair shares a head
+    double sn, cs;
+    sincos((double)positions[t] * inv_freq[d >> 1], &sn, &cs);
+    const float fc = (float)cs, fs = (float)sn;
+    y = (d & 1) ? fmaf(y, fc, other * fs) : fmaf(y, fc, -other * fs);
+  }
+  if (c < Cq) {
+    q_out[(int64_t)t * Cq + c] = from_f<TO>(y);
+    return;
+  }
+  const int where = slot_mapping ? slot_mapping[t] : -1;
+  if (where < 0) return;
+  const int page = where / page_size, off = where - page * page_size;
+  int g, e;
+  if (c < Cq + Ck) { g = (c - Cq) / D; e = (c - Cq) - g * D; }
+  else { g = (c - Cq - Ck) / Dv; e = D + (c - Cq - Ck) - g * Dv; }
+  pool[(((int64_t)page * nkv + g) * page_size + off) * (D + Dv) + e] = from_f<TO>(y);
+}
+
+__global__ void __launch_bounds__(256)
+conv_state_kernel(ConvSrc s, float* __restrict__ state, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                  const int* __restrict__ state_slots) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= s.C) return;
+  const int slot = state_slots[b];
+  if (slot < 0) return;
+  const int tok0 = cu_seqlens[b], n = cu_seqlens[b + 1] - tok0;
+  if (n <= 0) return;
+  const int start = context_lens[b] - n;
+  float* st = state + (int64_t)slot * (s.taps - 1) * s.C + c;
+  // Row k takes u at local index n - (taps-1) + k.  Old rows are read at k + n > k and rows are written in ascending
+  // order, so a thread never reads a row that it has replaced.
+  for (int k = 0; k < s.taps - 1; ++k) st[(int64_t)k * s.C] = conv_input(s, tok0, n - (s.taps - 1) + k, start, slot, c);
+}
+
+// proj: [T, >= C] float32 with C = nh*D + (own_kv ? nkv*(D+Dv) : 0) leading channels q|k|v.  bias: [C] or null.  wt: [C, taps]
+// or null (no convolution; taps is then 1).  state: [slots, taps-1, C] float32 (unused for taps == 1).  inv_freq: [rot/2]
+// float64.  q_out: [T, nh*D]; pool: cache rows of out_dtype (unused without own_kv).
+ME_API int me_conv_rope_kv(const float* proj, int64_t proj_stride, const float* bias, const float* wt, float* state, int taps,
+                           const double* inv_freq, int rot, const int* positions, const int* token_req, const int* cu_seqlens,
+                           const int* context_lens, const int* state_slots, const int* slot_mapping, void* q_out, void* pool,
+                           int out_dtype, int T, int B, int nh, int nkv, int D, int Dv, int own_kv, int page_size,
+                           cudaStream_t stream) {
+  if (T == 0) return 0;
+  ME_REQUIRE(T > 0 && B > 0 && nh > 0 && D > 0 && taps >= 1, "me_conv_rope_kv: bad sizes");
+  ME_REQUIRE(rot % 2 == 0 && rot >= 0 && rot <= D && (rot == 0 || D % 2 == 0), "me_conv_rope_kv: %d of %d elements rotated", rot, D);
+  ME_REQUIRE(taps == 1 || (state != nullptr && wt != nullptr), "me_conv_rope_kv: %d taps need weights and a state", taps);
+  ConvSrc s{proj, proj_stride, bias, state, nh * D + (own_kv ? nkv * (D + Dv) : 0), taps};
+  const int threads = s.C >= 256 ? 256 : 64;
+  dim3 grid(T, (s.C + threads - 1) / threads);
+  ME_DISPATCH_DTYPE(out_dtype, TO,
+                    me_launch(conv_rope_kv_kernel<TO>, grid, dim3(threads), 0, stream, s, wt, inv_freq, rot, positions, token_req,
+                              cu_seqlens, context_lens, state_slots, own_kv ? slot_mapping : (const int*)nullptr, (TO*)q_out,
+                              (TO*)pool, nh, own_kv ? nkv : 0, D, Dv, page_size));
+  ME_LAUNCH_CHECK("me_conv_rope_kv");
+  if (taps > 1) {
+    me_launch(conv_state_kernel, dim3(B, (s.C + threads - 1) / threads), dim3(threads), 0, stream, s, state, cu_seqlens,
+              context_lens, state_slots);
+    ME_LAUNCH_CHECK("me_conv_rope_kv (state)");
+  }
+  return 0;
+}

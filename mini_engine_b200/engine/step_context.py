@@ -64,6 +64,7 @@ class StepContext:
         self.on_replace = None         # called with a buffer's name before a larger one takes its place
         self.token_feedback = getattr(runner, "token_feedback", None)   # int32 on the device: a token id ~j in a step means entry j of it
         # Filled per step:
+        self.token_ids: torch.Tensor = None      # the step's token ids, for parts that look tokens up themselves
         self.positions: torch.Tensor = None
         self.token_req: torch.Tensor = None
         self.state_slots: torch.Tensor = None

@@ -16,6 +16,7 @@ from . import build as _build
 
 ATTN_TILE_Q = 16          # query tokens per block of the CUDA-core chunk kernel (csrc/attention_chunk.cu)
 ATTN_TILE_SIZES = (8, 16, 32, 64, 128)   # query tokens per block that some attention kernel may ask for
+SINK_ATTN_TILE_Q = 16     # query tokens per block of csrc/sink_attention.cu
 DECODE_PARTITION = 128    # keys per partition of the decode kernel (csrc/attention_decode.cu)
 MAX_HEAD_DIM = 256
 
@@ -51,6 +52,15 @@ _PROTOS = {
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
     "me_test_wait_expires": [_P, _I, _P, _P],
+    "me_sandwich_norm": [_P, _P, _I, _P, _F, _P, _F, _P, _I, _P, _I, _I, _I, _P],
+    "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P],
+    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
+    "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
+    "me_moe_combine": [_P, _L, _P, _P, _I, _P, _I, _L, _P, _I, _L, _I, _I, _P],
+    "me_token_side_gate": [_P, _I, _L, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _P],
 }
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -76,7 +86,8 @@ def require_extension() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = ctypes.c_int
-    if lib.me_attn_chunk_tile_q() != ATTN_TILE_Q or lib.me_attn_decode_partition() != DECODE_PARTITION:
+    if (lib.me_attn_chunk_tile_q() != ATTN_TILE_Q or lib.me_attn_decode_partition() != DECODE_PARTITION
+            or lib.me_sink_attn_tile_q() != SINK_ATTN_TILE_Q):
         raise KernelError("the kernel library and ops/__init__.py disagree on tile sizes")
     lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
     lib.me_attn_prefill_tcgen05_heads_per_block.argtypes = [_I, _I, _I, _I]
@@ -1162,3 +1173,145 @@ def batched_heads_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> Non
     with _Timed("library_bmm"):
         torch.bmm(x, w, out=out)
     library_calls += 1
+
+
+# ---- norms on both sides of a sub-layer, convolved and gated attention with a sink, routed feed-forwards ----------------
+def sandwich_norm(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor], mult: float,
+                  pre_weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+                  rows: Optional[torch.Tensor] = None, norm_out: bool = True) -> None:
+    """``residual += mult * y / rms(y) * post_weight`` (float32, in place; skipped without ``y``), then
+    ``out = residual / rms(residual) * pre_weight`` (``norm_out`` False: ``out`` is the new residual itself, in ``out``'s
+    dtype).  With ``rows`` only those rows are computed and ``residual`` is not written."""
+    T, W = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "sandwich_norm: the residual must be float32 [T, W]")
+    _need(y is None or (tuple(y.shape) == (T, W) and y.is_contiguous() and post_weight is not None), "sandwich_norm: y must be [T, W]")
+    for w in (post_weight, pre_weight):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == W and w.is_contiguous()), "sandwich_norm: weights are float32 [W]")
+    n = T if rows is None else rows.shape[0]
+    _need(out is None or (out.is_contiguous() and tuple(out.shape) == (n, W)), "sandwich_norm: output shape")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.is_contiguous()), "sandwich_norm: rows must be int32")
+    _call("me_sandwich_norm", residual.data_ptr(), _ptr(y), _dt(y) if y is not None else 0, _ptr(post_weight), float(mult),
+          _ptr(pre_weight), float(eps), _ptr(out), _dt(out) if out is not None else 0, _ptr(rows), n, W, 1 if norm_out else 0,
+          _stream())
+
+
+def clamped_glu(x: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """Rows [gate | up] -> ``g sigmoid(alpha g) (u + 1)`` with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    T, F2 = x.shape
+    _need(F2 % 2 == 0 and tuple(out.shape) == (T, F2 // 2) and x.stride(1) == 1 and out.stride(1) == 1, "clamped_glu: shapes")
+    _call("me_clamped_glu", x.data_ptr(), _dt(x), x.stride(0), out.data_ptr(), _dt(out), out.stride(0), T, F2 // 2, float(limit),
+          float(alpha), _stream())
+
+
+def conv_rope_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_weight: Optional[torch.Tensor],
+                 state: Optional[torch.Tensor], inv_freq: torch.Tensor, rot_dims: int, ctx, slot_mapping: Optional[torch.Tensor],
+                 q_out: torch.Tensor, pool: Optional[torch.Tensor], page_size: int, num_heads: int, num_kv_heads: int, dim: int,
+                 vdim: int, own_kv: bool) -> None:
+    """From the packed float32 projections q|k|v (the leading columns of ``proj``): bias, the short causal convolution with
+    its state, the rotation of neighbouring pairs, queries to ``q_out`` and keys and values into the cache rows that
+    ``slot_mapping`` names (see csrc/conv_rope_kv.cu).  Without ``own_kv`` only the queries exist."""
+    T = proj.shape[0]
+    C = num_heads * dim + (num_kv_heads * (dim + vdim) if own_kv else 0)
+    taps = conv_weight.shape[1] if conv_weight is not None else 1
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= C, "conv_rope_kv: projections must be float32 rows")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == C), "conv_rope_kv: bias must be float32 [channels]")
+    _need(conv_weight is None or (conv_weight.dtype == torch.float32 and conv_weight.is_contiguous() and conv_weight.shape[0] == C),
+          "conv_rope_kv: convolution weight must be float32 [channels, taps]")
+    _need(taps == 1 or (state is not None and state.dtype == torch.float32 and state.is_contiguous()
+                        and tuple(state.shape[1:]) == (taps - 1, C)), "conv_rope_kv: state must be float32 [slots, taps - 1, channels]")
+    _need(inv_freq.dtype == torch.float64 and inv_freq.numel() * 2 == rot_dims, "conv_rope_kv: inv_freq must be float64 [rot_dims / 2]")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, num_heads * dim), "conv_rope_kv: query output shape")
+    if own_kv:
+        _need(pool is not None and pool.is_contiguous() and pool.shape[-1] == dim + vdim and pool.dtype == q_out.dtype
+              and slot_mapping is not None, "conv_rope_kv: cache rows must hold dim + vdim values of the activations' dtype")
+    meta = ctx.attn_meta
+    _call("me_conv_rope_kv", proj.data_ptr(), proj.stride(0), _ptr(bias), _ptr(conv_weight), _ptr(state) if taps > 1 else 0, taps,
+          inv_freq.data_ptr(), rot_dims, ctx.positions.data_ptr(), ctx.token_req.data_ptr(), meta.cu_seqlens.data_ptr(),
+          meta.context_lens.data_ptr(), ctx.state_slots.data_ptr(), _ptr(slot_mapping) if own_kv else 0, q_out.data_ptr(),
+          _ptr(pool) if own_kv else 0, _dt(q_out), T, meta.num_reqs, num_heads, num_kv_heads, dim, vdim, 1 if own_kv else 0,
+          page_size, _stream())
+
+
+use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor cores where the sizes allow; a switch for comparisons
+
+
+def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, pool: torch.Tensor, page_size: int,
+                   block_tables: torch.Tensor, meta, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
+                   window: Optional[int], sink: bool) -> None:
+    """Attention over cache rows [key (dim) | value (vdim)]: ``q`` [T, heads * dim] -> ``out`` [T, heads * vdim]; a query at
+    position p sees keys p - window < j <= p; with ``sink`` the softmax's denominator has one more term, exp(0); ``gate``
+    (float32 rows of pre-activations, heads * vdim wide) multiplies the output by its sigmoid."""
+    T = q.shape[0]
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * dim and tuple(out.shape) == (T, num_heads * vdim),
+          "sink_attention: shapes")
+    _need(pool.dtype == q.dtype == out.dtype and pool.is_contiguous() and pool.shape[-1] == dim + vdim, "sink_attention: cache rows")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] == num_heads * vdim),
+          "sink_attention: the gate must be float32 rows")
+    _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "sink_attention: block tables")
+    tiles, n_tiles = meta.tile_lists[SINK_ATTN_TILE_Q]
+    _call("me_sink_attn", q.data_ptr(), _dt(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+          out.stride(0), pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
+          meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles, meta.num_decodes, num_heads, num_kv_heads, dim, vdim, page_size,
+          float(scale), int(window or 0), 1 if sink else 0, _stream())
+
+
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, weights: torch.Tensor) -> None:
+    """The ``top`` largest of every row of ``logits`` [T, E] + ``bias`` (float32) and the softmax over those only."""
+    T, E = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route: logits must be float32")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route: bias must be float32 [E]")
+    _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
+          and idx.is_contiguous() and weights.is_contiguous(), "moe_route: outputs are [T, top]")
+    _call("me_moe_route", logits.data_ptr(), _ptr(bias), T, E, top, idx.data_ptr(), weights.data_ptr(), _stream())
+
+
+def moe_sort(idx: torch.Tensor, num_experts: int, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor,
+             place: torch.Tensor) -> None:
+    """Group the (token, choice) pairs of ``idx`` [T, top] by expert: ``offsets`` [E + 1], ``order`` (pair ids in expert order,
+    token order inside an expert), ``place`` (where every pair went)."""
+    T, top = idx.shape
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (idx, counts, offsets, order, place)), "moe_sort: int32 tensors")
+    _need(counts.numel() >= num_experts and offsets.numel() >= num_experts + 1 and order.numel() >= T * top and place.numel() >= T * top,
+          "moe_sort: output sizes")
+    _call("me_moe_sort", idx.data_ptr(), T, top, num_experts, counts.data_ptr(), offsets.data_ptr(), order.data_ptr(),
+          place.data_ptr(), _stream())
+
+
+use_moe_mma = True        # bfloat16 expert products on the tensor cores where the sizes allow; a switch for comparisons
+
+
+def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, offsets: torch.Tensor,
+             out: torch.Tensor, glu: Optional[tuple[float, float]] = None) -> None:
+    """One product per expert: ``weight`` [E, N or 2N, K]; the rows of ``a`` are gathered through ``order`` (pair id // top) or,
+    without it, lie in expert order already; ``out`` [pairs, N] in expert order.  ``glu`` = (limit, alpha): the weight holds gate
+    rows then up rows and the result is the clamped gated activation."""
+    E, NN, K = weight.shape
+    N = NN // 2 if glu else NN
+    rows = out.shape[0]
+    _need(weight.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and out.stride(1) == 1 and out.shape[1] == N, "moe_gemm: shapes")
+    _need(order is not None or a.shape[0] == rows, "moe_gemm: rows in expert order")
+    limit, alpha = glu if glu else (0.0, 0.0)
+    _call("me_moe_gemm", a.data_ptr(), _dt(a), a.stride(0), _ptr(order), top, weight.data_ptr(), _dt(weight), weight.stride(0),
+          offsets.data_ptr(), E, out.data_ptr(), _dt(out), out.stride(0), rows, N, K, 1 if glu else 0, float(limit), float(alpha),
+          1 if use_moe_mma else 0, _stream())
+
+
+def moe_combine(rows: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """``out[t] = sum_k weights[t, k] * rows[place[t, k]]`` (+ ``shared[t]``); ``rows`` float32 in expert order."""
+    T, top = weights.shape
+    W = rows.shape[1]
+    _need(rows.dtype == torch.float32 and rows.stride(1) == 1 and tuple(out.shape) == (T, W) and out.stride(1) == 1, "moe_combine: shapes")
+    _need(shared is None or (tuple(shared.shape) == (T, W) and shared.stride(1) == 1), "moe_combine: the shared expert's output")
+    _call("me_moe_combine", rows.data_ptr(), rows.stride(0), place.data_ptr(), weights.data_ptr(), top, _ptr(shared),
+          _dt(shared) if shared is not None else 0, shared.stride(0) if shared is not None else 0, out.data_ptr(), _dt(out),
+          out.stride(0), T, W, _stream())
+
+
+def token_side_gate(z: torch.Tensor, token_ids: torch.Tensor, feedback: Optional[torch.Tensor], table: torch.Tensor, first: int,
+                    out: torch.Tensor) -> None:
+    """``out[t, j] = gelu_tanh(z[t, j]) * table[token_t, first + j]``."""
+    T, dim = z.shape
+    _need(z.stride(1) == 1 and out.is_contiguous() and tuple(out.shape) == (T, dim) and table.is_contiguous(), "token_side_gate: shapes")
+    _need(token_ids.dtype == torch.int32 and token_ids.numel() == T, "token_side_gate: token ids must be int32 [T]")
+    _call("me_token_side_gate", z.data_ptr(), _dt(z), z.stride(0), token_ids.data_ptr(), _ptr(feedback), table.data_ptr(), _dt(table),
+          table.stride(0), table.shape[0], first, dim, out.data_ptr(), _dt(out), T, _stream())

@@ -1,4 +1,4 @@
-from .base import (AddedToResidual, PendingNorm, Upcoming, DiskSource, FeedForward, KVCacheNeed, Mixer, Norm, ParamDecl, Part,
+from .base import (AddedToResidual, NormedUpdate, PendingNorm, Upcoming, DiskSource, FeedForward, KVCacheNeed, Mixer, Norm, ParamDecl, Part,
                    PositionEncoding, StateNeed, StreamUpdate)
 from .registry import (PartSpec, build_block, build_part, register_block, register_feed_forward, register_mixer,
                        register_norm, register_position_encoding, registered)
@@ -11,6 +11,9 @@ from .conv import CausalShortConv
 from .polynorm_mlp import PolyNormMLP
 from .latent_attention import LatentAttention
 from .mlstm import MLSTM
+from .sink_attention import SinkAttention
+from .glu_mlp import ClampedGLU, RoutedExperts
+from .token_side import TokenSideInput
 from .embed import LMHead, TokenEmbedding
-from .block import Block, BlockSpec, HyperConnectionBlock, PreNormBlock, SharedRef
+from .block import Block, BlockSpec, HyperConnectionBlock, PreNormBlock, SandwichNormBlock, SharedRef
 from .model import DecoderModel, LayerCall, ModelPlan

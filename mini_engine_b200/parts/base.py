@@ -72,6 +72,17 @@ class StreamUpdate:
 
 
 @dataclass
+class NormedUpdate:
+    """What a block whose sub-layers are normalised on both sides returns instead of a plain output: ``y`` [T, width] has
+    not joined the residual stream yet; the next kernel that reads the stream (the next norm, or the model's last) first
+    computes x <- x + mult * y / rms(y) * weight, with ``weight`` the float32 weight of the norm behind the sub-layer."""
+    y: "torch.Tensor"
+    weight: "torch.Tensor"
+    eps: float
+    mult: float
+
+
+@dataclass
 class AddedToResidual:
     """What a part returns instead of its output when its last kernel has already added that output into the
     float32 residual stream; ``sumsq`` [parts, T] holds the new residual's sums of squares per strip of

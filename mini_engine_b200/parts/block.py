@@ -10,7 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
-from .base import ParamDecl, Part, StreamUpdate, Upcoming
+from .base import NormedUpdate, ParamDecl, Part, StreamUpdate, Upcoming
 from .registry import PartSpec, build_part, register_block
 
 
@@ -180,6 +180,59 @@ class HyperConnectionBlock(Block):
     fuse_decode_conv = True      # a switch for comparisons
 
 
+class SandwichNormBlock(Block):
+    """A block whose sub-layers are normalised on both sides: x <- x + mult * norm_b(sublayer(norm_a(x))) for the mixer
+    and then for the feed-forward (which may be absent), and after them, optionally, a per-layer input from the token
+    itself: x <- x + mult * rms_norm(side(x)) with a plain weight.  Each of these sums is left pending (``NormedUpdate``)
+    and done by the kernel that reads the stream next: the following norm, or the copy of the stream that the token
+    input reads.
+
+    ``BlockSpec.args``: ``mult``; ``width``; ``post_mixer_norm`` / ``post_feed_forward_norm`` (the ``PartSpec`` of the norm
+    behind each sub-layer); ``side`` = {dim, first, table: SharedRef} or absent."""
+    capturable = True
+    feed_forward_optional = True
+
+    def __init__(self, spec: BlockSpec, shared: Optional[dict] = None):
+        super().__init__(spec, shared)
+        from .token_side import TokenSideInput
+        a = spec.args
+        self.mult = float(a.get("mult", 1.0))
+        self.post_mixer_norm = build_part("norm", a["post_mixer_norm"])
+        self.post_feed_forward_norm = build_part("norm", a["post_feed_forward_norm"]) if self.feed_forward is not None else None
+        self.side = None
+        if a.get("side"):
+            side = a["side"]
+            table = (shared or {}).get(side["table"].key) if isinstance(side["table"], SharedRef) else side["table"]
+            if table is None:
+                raise ValueError("a block's token input needs the model's table (ModelPlan.tables)")
+            self.side = TokenSideInput(a["width"], side["dim"], side["first"], table)
+
+    def sub_parts(self):
+        parts = super().sub_parts() + [("", self.post_mixer_norm)]
+        if self.post_feed_forward_norm is not None:
+            parts.append(("", self.post_feed_forward_norm))
+        if self.side is not None:
+            parts.append(("", self.side))
+        return parts
+
+    def upcoming(self) -> Upcoming:
+        return Upcoming(self.mixer_norm, self.mixer.first_weight())
+
+    def forward(self, residual, delta, ctx, call, upcoming=None):
+        from .. import ops
+        eps = self.mixer_norm.eps
+        y = self.mixer.forward(self.mixer_norm.forward(residual, delta, ctx), ctx, call)
+        update = NormedUpdate(y, self.post_mixer_norm.weight, eps, self.mult)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(self.feed_forward_norm.forward(residual, update, ctx), ctx)
+            update = NormedUpdate(y, self.post_feed_forward_norm.weight, eps, self.mult)
+        if self.side is not None:
+            x = ctx.buffer("stream_copy", tuple(residual.shape), ctx.act_dtype)
+            ops.sandwich_norm(residual, update.y, update.weight, update.mult, None, eps, x, norm_out=False)
+            update = NormedUpdate(self.side.forward(x, ctx), self.side.p(self.side.norm), eps, self.mult)
+        return update
+
+
 @dataclass(frozen=True)
 class SharedRef:
     """Stands in a PartSpec's args for an object that the model builds once and shares."""
@@ -188,3 +241,4 @@ class SharedRef:
 
 register_block("pre_norm", PreNormBlock)
 register_block("hyper_connection", HyperConnectionBlock)
+register_block("sandwich_norm", SandwichNormBlock)

@@ -1,0 +1,109 @@
+"""Gated feed-forwards whose two halves are clamped, dense or as a mixture of routed experts.
+
+One expert (and the dense form): g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
+y = g * sigmoid(alpha * g) * (u + 1), output W_down y; ``limit`` None: nothing is clamped.
+
+``RoutedExperts``: router logits z = W_router h + b in float32; the ``top`` experts with the largest logits are chosen
+and weighted by the softmax over the chosen logits only; the output is the weighted sum of their outputs, plus a
+``shared`` expert (same form, sizes of its own) that runs for every token.  Routing, grouping by expert, the per-expert
+products and the weighted sum all run on the device, so a step's shape does not depend on the routing.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import DiskSource, FeedForward, ParamDecl
+from .linear import Linear
+from .registry import register_feed_forward
+
+
+class ClampedGLU(FeedForward):
+    capturable = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: Optional[float] = None, alpha: float = 1.702,
+                 gate: str = "gate", up: str = "up", down: str = "down"):
+        super().__init__()
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.limit = float(limit) if limit is not None else 0.0
+        self.alpha = float(alpha)
+        self.gate_up = Linear(hidden_size, [(gate, intermediate_size), (up, intermediate_size)], name="gate_up")
+        self.down = Linear(intermediate_size, [(down, hidden_size)], name=down)
+
+    def sub_parts(self):
+        return [("", self.gate_up), ("", self.down)]
+
+    def first_weight(self):
+        return self.gate_up.weight
+
+    def forward(self, x, ctx, out_name: str = "ffn_out", out_dtype=None):
+        z = self.gate_up.forward(x, ctx, out_name + "_gate_up")
+        act = ctx.buffer(out_name + "_act", (z.shape[0], self.intermediate_size), ctx.act_dtype)
+        ops.clamped_glu(z, act, self.limit, self.alpha)
+        return self.down.forward(act, ctx, out_name, out_dtype=out_dtype)
+
+
+class RoutedExperts(FeedForward):
+    capturable = True
+
+    def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, limit: Optional[float] = None,
+                 alpha: float = 1.702, router_bias: bool = True, shared: Optional[dict] = None):
+        super().__init__()
+        if not 1 <= top <= num_experts:
+            raise ValueError(f"{top} of {num_experts} experts cannot be chosen")
+        self.hidden_size, self.num_experts, self.top, self.expert_size = hidden_size, num_experts, top, expert_size
+        self.limit = float(limit) if limit is not None else 0.0
+        self.alpha = float(alpha)
+        self.has_router_bias = router_bias
+        self.router = Linear(hidden_size, [("router", num_experts)], name="router")
+        self.shared = ClampedGLU(hidden_size, **shared) if shared else None
+        self._gate_up = self._down = None
+
+    def sub_parts(self):
+        return [("", self.router)] + ([("shared.", self.shared)] if self.shared is not None else [])
+
+    def param_decls(self):
+        E, F, W = self.num_experts, self.expert_size, self.hidden_size
+        gate_up, down = [], []
+        for e in range(E):
+            gate_up += [DiskSource(f"e{e}.gate", 2 * F * e, F), DiskSource(f"e{e}.up", 2 * F * e + F, F)]
+            down.append(DiskSource(f"e{e}.down", W * e, W))
+        decls = [ParamDecl("experts_gate_up", (E * 2 * F, W), sources=gate_up), ParamDecl("experts_down", (E * W, F), sources=down)]
+        if self.has_router_bias:
+            decls.append(ParamDecl("router.b", (E,), role="vector"))
+        return decls
+
+    def first_weight(self):
+        return self.router.weight
+
+    def finalize(self, dtype, device):
+        E, F, W = self.num_experts, self.expert_size, self.hidden_size
+        self._gate_up = self.p("experts_gate_up").view(E, 2 * F, W)
+        self._down = self.p("experts_down").view(E, W, F)
+
+    def forward(self, x, ctx):
+        E, F, W, top = self.num_experts, self.expert_size, self.hidden_size, self.top
+        T = x.shape[0]
+        z = self.router.forward(x, ctx, "moe_logits", out_dtype=torch.float32)
+        idx = ctx.buffer("moe_idx", (T, top), torch.int32)
+        wgt = ctx.buffer("moe_weights", (T, top), torch.float32)
+        ops.moe_route(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt)
+        counts = ctx.buffer("moe_counts", (E,), torch.int32)
+        offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32)
+        order = ctx.buffer("moe_order", (T * top,), torch.int32)
+        place = ctx.buffer("moe_place", (T * top,), torch.int32)
+        ops.moe_sort(idx, E, counts, offsets, order, place)
+        act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)
+        ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha))
+        rows = ctx.buffer("moe_rows", (T * top, W), torch.float32)
+        ops.moe_gemm(act, None, top, self._down, offsets, rows)
+        shared = self.shared.forward(x, ctx, out_name="moe_shared") if self.shared is not None else None
+        out = ctx.buffer("ffn_out", (T, W), ctx.act_dtype)
+        ops.moe_combine(rows, place, wgt, shared, out)
+        return out
+
+
+register_feed_forward("clamped_glu", ClampedGLU)
+register_feed_forward("routed_experts", RoutedExperts)

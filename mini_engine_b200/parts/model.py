@@ -26,6 +26,7 @@ class LayerCall:
     block: int
     cache_slot: int
     writes_cache: bool = True
+    kv_slot: "Optional[int]" = None    # a mixer that reads ANOTHER call's keys and values: the cache slot that holds them
 
 
 @dataclass
@@ -45,6 +46,8 @@ class ModelPlan:
     embed_param: str = "weight"        # the tensors' names behind those prefixes
     head_param: str = "weight"
     embedding_scale: float = 1.0       # the embedding's rows are multiplied by this
+    tables: dict[str, tuple[str, int, int]] = field(default_factory=dict)   # key -> (tensor name, rows, columns): tables
+                                       # indexed by token that blocks share (``SharedRef(key)`` in a ``BlockSpec``'s args)
     streams: int = 1                   # residual streams; > 1: the residual is [streams, T, hidden], all equal at the start
 
 
@@ -57,6 +60,8 @@ class DecoderModel(Part):
         self.shared = {k: build_part("position_encoding", s) for k, s in plan.shared.items()}
         self.embed = TokenEmbedding(plan.vocab_size, plan.hidden_size, scale=plan.embedding_scale, streams=plan.streams,
                                     param=plan.embed_param)
+        self.tables = {k: TokenEmbedding(rows, cols, param=name) for k, (name, rows, cols) in plan.tables.items()}
+        self.shared.update(self.tables)
         self.blocks = [build_block(s, self.shared) for s in plan.blocks]
         self.final_norm = build_part("norm", plan.final_norm)
         tied = plan.embed_prefix + plan.embed_param if plan.tie_word_embeddings else None
@@ -78,10 +83,13 @@ class DecoderModel(Part):
                 written.add(c.cache_slot)
             elif c.cache_slot not in written:
                 raise ValueError(f"cache slot {c.cache_slot} is read before any call writes it")
+            if c.kv_slot is not None and c.kv_slot not in written:
+                raise ValueError(f"cache slot {c.kv_slot} is read (kv_slot) before any call writes it")
 
     # ---- structure -----------------------------------------------------------------
     def sub_parts(self):
         parts = [(self.plan.embed_prefix, self.embed)]
+        parts += [("", t) for t in self.tables.values()]
         parts += [(self.plan.block_prefix.format(i=i), b) for i, b in enumerate(self.blocks)]
         parts += [(self.plan.final_norm_prefix, self.final_norm), (self.plan.head_prefix, self.head)]
         return parts
@@ -107,6 +115,7 @@ class DecoderModel(Part):
     # ---- one step ------------------------------------------------------------------
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         """Hidden states of the wanted rows, normalised: ``[len(ctx.logits_rows), hidden]``."""
+        ctx.token_ids = token_ids
         residual = self.embed.forward(token_ids, ctx)
         delta = None
         for i, call in enumerate(self.schedule):

@@ -13,34 +13,53 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import AddedToResidual, Norm, ParamDecl, PendingNorm, StreamUpdate
+from .base import AddedToResidual, Norm, NormedUpdate, ParamDecl, PendingNorm, StreamUpdate
 from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    """``param``: the weight's name on disk, for models that do not call it ``weight``.  ``unit_offset``: the weight is
+    stored as its distance from one (y = x / rms(x) * (1 + w)); the sum is formed once, in float32, when the weights
+    are in place.  A pending ``NormedUpdate`` (a sub-layer's output that is itself normalised, weighted and scaled before
+    it joins the stream) goes into the residual in the same pass."""
     capturable = True
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, param: str = "weight", unit_offset: bool = False):
         super().__init__()
         self.size = size
         self.eps = float(eps)
+        self.param = param
+        self.unit_offset = unit_offset
+        self._weight = None
 
     def param_decls(self):
-        return [ParamDecl("weight", (self.size,), init="norm", role="vector")]
+        return [ParamDecl(self.param, (self.size,), init="normal" if self.unit_offset else "norm", role="vector")]
+
+    def finalize(self, dtype, device):
+        self._weight = (1.0 + self.p(self.param)).contiguous() if self.unit_offset else self.p(self.param)
+
+    @property
+    def weight(self) -> torch.Tensor:
+        """The factor that multiplies the normalised rows (float32)."""
+        return self._weight if self._weight is not None else self.p(self.param)
 
     def separable_weight(self):
         """y = x * rsqrt(mean(x^2) + eps) * w splits into an element-wise x * w and one factor per row, so the part
         in front may write x * w itself."""
-        return self.p("weight")
+        return self.weight
 
     def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False):
-        if isinstance(delta, AddedToResidual):
-            if lazy and rows is None and delta.preweighted is not None and delta.weight is self.p("weight"):
-                return PendingNorm(residual, self.p("weight"), self.eps, delta.sumsq, delta.preweighted)
-            delta = None                          # the residual already holds the sum
         n = residual.shape[0] if rows is None else rows.shape[0]
+        if isinstance(delta, NormedUpdate):
+            out = ctx.buffer("norm_out", (n, self.size), ctx.act_dtype)
+            ops.sandwich_norm(residual, delta.y, delta.weight, delta.mult, self.weight, self.eps, out, rows=rows)
+            return out
+        if isinstance(delta, AddedToResidual):
+            if lazy and rows is None and delta.preweighted is not None and delta.weight is self.weight:
+                return PendingNorm(residual, self.weight, self.eps, delta.sumsq, delta.preweighted)
+            delta = None                          # the residual already holds the sum
         out = ctx.buffer("norm_out", (n, self.size), ctx.act_dtype)
-        ops.add_rmsnorm(residual, delta, self.p("weight"), self.eps, out, rows=rows)
+        ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows=rows)
         return out
 
 
