@@ -87,9 +87,11 @@ def windowed_sink_attention(q, k, v, scale, window):
 
 
 def clamped_glu(h, w, pre, limit):
-    """g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g sigmoid(1.702 g) (u + 1), out = W_down y."""
-    g = (h @ w[pre + "gate"].T).clamp(max=limit)
-    u = (h @ w[pre + "up"].T).clamp(-limit, limit)
+    """g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g sigmoid(1.702 g) (u + 1), out = W_down y
+    (``limit`` None: nothing is clamped)."""
+    g, u = h @ w[pre + "gate"].T, h @ w[pre + "up"].T
+    if limit is not None:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
     return (g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[pre + "down"].T
 
 
@@ -135,15 +137,15 @@ def routed_experts(h, w, pre, mlp):
         chosen = torch.topk(z[t], top).indices
         p = torch.softmax(z[t, chosen], 0)
         for e, pe in zip(chosen.tolist(), p):
-            out[t] += pe * clamped_glu(h[t:t + 1], w, f"{pre}e{e}.", mlp["expert"]["limit"])[0]
+            out[t] += pe * clamped_glu(h[t:t + 1], w, f"{pre}e{e}.", mlp["expert"].get("limit"))[0]
     if mlp.get("shared"):
-        out = out + clamped_glu(h, w, pre + "shared.", mlp["shared"]["limit"])
+        out = out + clamped_glu(h, w, pre + "shared.", mlp["shared"].get("limit"))
     return out
 
 
 def feed_forward(h, w, pre, mlp):
     if mlp["kind"] == "dense":
-        return clamped_glu(h, w, pre, mlp["limit"])
+        return clamped_glu(h, w, pre, mlp.get("limit"))
     return routed_experts(h, w, pre, mlp)
 
 
