@@ -28,8 +28,8 @@ GPU: for ``--gpus N`` with N > 1 one line says so and the exit code is 2.
 Modes: ``step`` (the line above), ``offline`` (the reference's own bench.py:38-66 with its options ``--num-seqs
 --budget --chunked --threshold --out --label --expect-gpu``; a JSON row like the reference's is appended to
 ``--out``), ``mixed`` (the 8B workload above, at any shape), ``decode`` (decode at batches ``--batches`` after
-``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen`` (prefill and decode of the
-Logozen design at the layer sizes ``--sizes``, beside the Qwen3 of equal size, with the time of every kernel).
+``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen`` and ``pugadra``
+(prefill and decode of that design at the layer sizes ``--sizes``, beside the Qwen3 of equal size, with the time of every kernel).
 """
 from __future__ import annotations
 
@@ -85,6 +85,35 @@ LOGOZEN_SIZES = {   # width, layers, ff, attention heads / dim / rot_dim / vdim 
     "m": _logozen(2048, 8, 8192, 16, 64, 64, 128, 256, 8, 128, 256),
     "l": _logozen(4096, 6, 12288, 32, 64, 64, 128, 512, 16, 128, 256),
 }
+
+
+def _pugadra(width, layers, ff, heads, kv_heads, dim, window, experts, top, expert_ff, shared_ff, side, vocab=32768, taps=3):
+    """A Pugadra of ``layers`` layers: even layers have keys and values of their own and a dense feed-forward, odd layers
+    take the keys of the layer before and route ``top`` of ``experts`` experts beside a shared one; and the Qwen3 of the same
+    width, depth, heads, head size, window, feed-forward width and vocabulary to set beside it."""
+    def mixer(i):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": taps, "rot": {"base": 10000.0, "dims": dim},
+             "mask": {"size": window}, "scale": dim ** -0.5}
+        if i % 2:
+            m["kv_from"] = i - 1
+        return m
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    cfg = {"architecture": "Pugadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.3,
+           "token_side": {"dim": side},
+           "layers": [{"type": "attention", "mixer": mixer(i), "mlp": moe if i % 2 else {"kind": "dense", "ff": ff, "limit": 7.0}}
+                      for i in range(layers)]}
+    twin = _qwen3(layers, width, heads, kv_heads, ff, True, head_dim=dim, vocab_size=vocab, use_sliding_window=True,
+                  sliding_window=window, max_window_layers=0)
+    return cfg, twin
+
+
+PUGADRA_SIZES = {   # width, layers, ff, heads / kv heads / head size, window, experts / chosen / expert ff / shared ff, token input
+    "s": _pugadra(1024, 8, 3072, 16, 4, 64, 512, 16, 2, 768, 768, 64),
+    "m": _pugadra(2048, 8, 8192, 16, 4, 128, 1024, 32, 2, 2048, 2048, 128),
+    "l": _pugadra(4096, 6, 12288, 32, 8, 128, 1024, 32, 4, 2048, 4096, 256),
+}
+DESIGN_SIZES = {"logozen": LOGOZEN_SIZES, "pugadra": PUGADRA_SIZES}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
@@ -94,8 +123,8 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen"], default="step")
-    p.add_argument("--sizes", default="s,m", help="logozen mode: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
+    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen", "pugadra"], default="step")
+    p.add_argument("--sizes", default="s,m", help="logozen and pugadra modes: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
     p.add_argument("--shape", choices=sorted(SHAPES), default="0.6b", help="layer sizes, when no --model is given")
     p.add_argument("--extras", type=int, default=1,
                    help="step mode: also run the offline workload, the 8B mixed workload and the 32B decode points")
@@ -670,12 +699,16 @@ def _logozen_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
         else:
             need["me_mlstm_scan"] += 4.0 * m["heads"] * m["dim"] * m["vdim"] * T
     need["me_hc_norm"] += W * (4 * S + item)                               # the last norm, one row
+    return _fractions(need, ("me_latent_attention_mma", "me_mlstm_scan"), times, pk)
+
+
+def _fractions(need: dict, flop_kernels, times: dict, pk: dict) -> dict:
     out = {}
     for name, amount in need.items():
         us = times.get(name, {}).get("us")
         if not us or not amount:
             continue
-        flops = name in ("me_latent_attention_mma", "me_mlstm_scan")
+        flops = name in flop_kernels
         rate = amount / (us * 1e-6)
         out[name] = {"us": us, ("flops" if flops else "bytes"): amount,
                      "frac": round(rate / (pk["bf16_tflops"] * 1e12 if flops else pk["hbm_gbs"] * 1e9), 4),
@@ -683,18 +716,68 @@ def _logozen_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
     return out
 
 
-def run_logozen_mode(args) -> int:
-    """Prefill and decode throughput of Logozen at layer sizes that resemble real models', beside the Qwen3 of the same
+def _window_pairs(T: int, window) -> float:
+    """(query, key) pairs of a prompt of T tokens under a window."""
+    if not window or window >= T:
+        return T * (T + 1) / 2
+    return window * (window + 1) / 2 + (T - window) * window
+
+
+def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
+    """What Pugadra's own kernels have to move or do in a prefill step of T tokens and the fraction of the measured peak
+    that their summed time makes: bytes for the element-wise kernels, multiply-adds for attention and the experts."""
+    W = cfg["width"]
+    side = cfg.get("token_side", {}).get("dim", 0)
+    need = {k: 0.0 for k in ("me_sandwich_norm", "me_conv_rope_kv", "me_sink_attn", "me_sink_attn_mma", "me_clamped_glu", "me_moe_gemm",
+                             "me_moe_combine", "me_token_side_gate")}
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        own = "kv_from" not in m
+        subs = 1 + (mlp is not None) + (1 if side else 0)
+        need["me_sandwich_norm"] += subs * T * W * (8 + 2 * item)          # stream read and written, y read, h written
+        C = H * D + (G * (D + V) if own else 0)
+        need["me_conv_rope_kv"] += T * C * (4 + item)
+        att = 2.0 * H * (D + V) * _window_pairs(T, m.get("mask", {}).get("size"))
+        need["me_sink_attn"] += att
+        need["me_sink_attn_mma"] += att
+        if mlp is not None and mlp["kind"] == "dense":
+            need["me_clamped_glu"] += T * mlp["ff"] * 3 * item
+        elif mlp is not None:
+            need["me_moe_gemm"] += 6.0 * T * mlp["router"]["top"] * mlp["expert"]["ff"] * W
+            need["me_moe_combine"] += T * W * (4 * mlp["router"]["top"] + 2 * item)
+            if mlp.get("shared"):
+                need["me_clamped_glu"] += T * mlp["shared"]["ff"] * 3 * item
+        if side:
+            need["me_token_side_gate"] += T * side * (4 + 2 * item)
+    return _fractions(need, ("me_sink_attn", "me_sink_attn_mma", "me_moe_gemm"), times, pk)
+
+
+def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
+    """The like kernels of the Qwen3 beside a design: its norm, its q/k preparation and its prompt attention."""
+    W, L = cfg["hidden_size"], cfg["num_hidden_layers"]
+    H, G, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    window = cfg.get("sliding_window") if cfg.get("use_sliding_window") else None
+    att = 4.0 * H * D * _window_pairs(T, window) * L
+    need = {"me_add_rmsnorm": 2 * L * T * W * (8 + 2 * item), "me_qk_norm_rope_kv_write": L * T * (H + 2 * G) * D * 2 * item,
+            "me_attn_prefill_tcgen05": att, "me_attn_prefill": att}
+    return _fractions(need, ("me_attn_prefill_tcgen05", "me_attn_prefill"), times, pk)
+
+
+def run_design_mode(args, design: str) -> int:
+    """Prefill and decode throughput of a design at layer sizes that resemble real models', beside the Qwen3 of the same
     width, depth, heads, feed-forward width and vocabulary; random weights drawn on the device."""
     import torch
+    sizes_of = DESIGN_SIZES[design]
+    roofline = {"logozen": _logozen_roofline, "pugadra": _pugadra_roofline}[design]
     pk = peaks()
     item = 2 if args.dtype in ("bfloat16", "bf16") else 4
     T = args.prompt_len or 2048
     batches = [int(b) for b in args.batches.split(",") if b]
     rows = {}
     for size in [x for x in args.sizes.split(",") if x]:
-        cfg, twin = LOGOZEN_SIZES[size]
-        for label, c in (("logozen", cfg), ("qwen3", twin)):
+        cfg, twin = sizes_of[size]
+        for label, c in ((design, cfg), ("qwen3", twin)):
             model = Model.of_config(c, f"{label} {size}", args.seed)
             top = max(batches)
             llm = make_engine(model, args, max_seqs=top + 2, budget=max(T, top), context=T + 256,   # (a state slot each, and the prompt's)
@@ -710,13 +793,12 @@ def run_logozen_mode(args) -> int:
             times = _kernel_times(runner, cache, prompt, prompts[:min(8, top)])
             row["kernels_prefill_us"] = times["prefill"]
             row["kernels_decode_b8_us"] = times["decode"]
-            if label == "logozen":
-                row["roofline_prefill"] = _logozen_roofline(c, T, item, pk, times["prefill"])
+            row["roofline_prefill"] = (roofline if label == design else _qwen3_roofline)(c, T, item, pk, times["prefill"])
             rows[f"{label}_{size}"] = row
             del llm, runner, cache
             release_memory()
-    print(json.dumps({"mode": "logozen", "dtype": args.dtype, "peaks": pk["source"], "prompt_tokens": T,
-                      "decode_context": T // 2, "sizes": {k: {"logozen": v[0], "qwen3": v[1]} for k, v in LOGOZEN_SIZES.items()
+    print(json.dumps({"mode": design, "dtype": args.dtype, "peaks": pk["source"], "prompt_tokens": T,
+                      "decode_context": T // 2, "sizes": {k: {design: v[0], "qwen3": v[1]} for k, v in sizes_of.items()
                                                           if k in args.sizes.split(",")}, "results": rows}))
     return 0
 
@@ -949,8 +1031,8 @@ def main() -> int:
         return run_decode_mode(args)
     if args.mode == "prefill":
         return run_prefill_mode(args)
-    if args.mode == "logozen":
-        return run_logozen_mode(args)
+    if args.mode in DESIGN_SIZES:
+        return run_design_mode(args, args.mode)
     return run_step_mode(args)
 
 

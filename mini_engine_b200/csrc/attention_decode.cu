@@ -833,7 +833,8 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const int* __restrict__ cu_seqlens,
                                     const int* __restrict__ context_lens,
                                     const float* __restrict__ tmp_out, const float* __restrict__ tmp_m,
-                                    const float* __restrict__ tmp_l, int nh, int hd, int max_parts, int part_keys) {
+                                    const float* __restrict__ tmp_l, int nh, int hd, int max_parts, int part_keys,
+                                    int sink, const float* __restrict__ gate, int64_t gate_stride) {
   constexpr int CHUNK = 128;                         // partitions whose factors are held in shared memory at a time
   __shared__ float f_s[CHUNK], red[32];
   const int b = blockIdx.x, h = blockIdx.y;
@@ -854,10 +855,10 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
       lv[p] = p < P ? tmp_l[row0 + p] : 0.f;
       ov[p] = (p < P && tid < hd) ? tmp_out[(row0 + p) * hd + tid] : 0.f;     // (never written where mv is -inf: not used then)
     }
-    float M = -INFINITY;
+    float M = sink ? 0.f : -INFINITY;                // the sink: a key of score 0 that has no value
 #pragma unroll
     for (int p = 0; p < 16; ++p) M = fmaxf(M, mv[p]);
-    float lt = 0.f, acc = 0.f;
+    float lt = sink ? expf(-M) : 0.f, acc = 0.f;
 #pragma unroll
     for (int p = 0; p < 16; ++p) {                   // partitions in index order
       if (mv[p] == -INFINITY) continue;
@@ -865,7 +866,11 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
       lt += f * lv[p];
       acc += f * ov[p];
     }
-    if (tid < hd) out[tok * out_row_stride + (int64_t)h * hd + tid] = from_f<T>(lt > 0.f ? acc / lt : 0.f);
+    if (tid < hd) {
+      float v = lt > 0.f ? acc / lt : 0.f;
+      if (gate) v = v / (1.f + expf(-gate[tok * gate_stride + (int64_t)h * hd + tid]));
+      out[tok * out_row_stride + (int64_t)h * hd + tid] = from_f<T>(v);
+    }
     return;
   }
   // the largest maximum: a partition per thread, then lanes, then warps
@@ -874,9 +879,9 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
   mx = warp_max(mx);
   if (lane == 0) red[warp] = mx;
   __syncthreads();
-  float M = -INFINITY;
+  float M = sink ? 0.f : -INFINITY;
   for (int w = 0; w < nwarps; ++w) M = fmaxf(M, red[w]);
-  float lt = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};      // thread t owns columns t, t + blockDim, ... (hd <= 4 blockDim)
+  float lt = sink ? expf(-M) : 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};      // thread t owns columns t, t + blockDim, ... (hd <= 4 blockDim)
   for (int p0 = 0; p0 < P && M > -INFINITY; p0 += CHUNK) {
     const int n = min(CHUNK, P - p0);
     __syncthreads();
@@ -934,7 +939,11 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const int d = tid + c * (int)blockDim.x;
-    if (d < hd) o[d] = from_f<T>(lt > 0.f ? acc[c] / lt : 0.f);
+    if (d < hd) {
+      float v = lt > 0.f ? acc[c] / lt : 0.f;
+      if (gate) v = v / (1.f + expf(-gate[tok * gate_stride + (int64_t)h * hd + d]));
+      o[d] = from_f<T>(v);
+    }
   }
 }
 
@@ -957,7 +966,8 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
                           int bt_stride, const int* cu_seqlens, const int* context_lens,
                           int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                           int window, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts,
-                          int* err, int kind, const void* kv_map, cudaStream_t stream) {
+                          int* err, int kind, const void* kv_map, int sink, const float* gate, int64_t gate_stride,
+                          cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 256, "me_attn_decode: head_dim %d is not a multiple of 8 up to 256", hd);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode: %d heads, %d kv heads", nh, nkv);
@@ -1012,7 +1022,8 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   dim3 mgrid(num_reqs, nh);
   const int mthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(decode_merge_kernel<T>, mgrid, dim3(mthreads), 0, stream,
-      (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART)));
+      (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART, sink, gate,
+      gate_stride)));
   ME_LAUNCH_CHECK("me_attn_decode (merge)");
   return 0;
 }
@@ -1081,7 +1092,7 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");
   dim3 mgrid(num_reqs, nh);
   me_launch(decode_merge_kernel<bf16>, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream, (bf16*)out, out_row_stride, cu_seqlens,
-            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART * tiles);
+            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART * tiles, 0, (const float*)nullptr, (int64_t)0);
   ME_LAUNCH_CHECK("me_attn_decode_fused (merge)");
   return 0;
 }

@@ -47,7 +47,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                             bf16* __restrict__ out, int64_t out_row_stride, const int* __restrict__ block_tables,
                             int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                             const int* __restrict__ tiles, int nh, int nkv, int gp, int page_size, float scale_log2,
-                            int window, int* __restrict__ err) {
+                            int window, int sink, const float* __restrict__ gate, int64_t gate_stride, int* __restrict__ err) {
   constexpr int HALVES = HD / 64;
   constexpr int Q_BYTES = TA_ROWS * HD * 2, KV_BYTES = TA_KEYS * HD * 2, P_BYTES = TA_ROWS * TA_KEYS * 2;
   constexpr int HALF_BYTES = 128 * 128;                 // one [128][64] bfloat16 block
@@ -318,6 +318,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     if (half == 0) l_other[r] = l;
     asm volatile("bar.sync 1, 256;\n" ::: "memory");
     l = l_other[r];
+    if (sink) l += ex2(-(m == neg_inf ? 0.f : m) * scale_log2);         // a key of score 0 that has no value
     if (ok) ok = tma::mbar_wait(&o_ready, (n_tiles - 1) & 1);          // the last P V is done
     float o_acc[OC];
     if (ok) {
@@ -329,6 +330,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     if (ok && row_ok) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (int64_t)(tok0 + q0 + tk) * out_row_stride + (int64_t)(head0 + hh) * HD + half * OC;
+      if (gate) {                                            // the output times the sigmoid of the gate's pre-activation
+        const float* gr = gate + (int64_t)(tok0 + q0 + tk) * gate_stride + (int64_t)(head0 + hh) * HD + half * OC;
+#pragma unroll
+        for (int jj = 0; jj < OC; ++jj) o_acc[jj] = __fdividef(o_acc[jj], 1.f + __expf(-gr[jj]));
+      }
 #pragma unroll
       for (int q = 0; q < OC / 8; ++q) {
         uint4 pk;
@@ -371,7 +377,8 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
                                        bf16* __restrict__ out, int64_t out_row_stride, const int* __restrict__ block_tables,
                                        int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                                        const int* __restrict__ tiles, int nh, int nkv, int gp, int page_size, float scale_log2,
-                                       int window, int* __restrict__ err) {
+                                       int window, int sink, const float* __restrict__ gate, int64_t gate_stride,
+                                       int* __restrict__ err) {
   constexpr int KEYS = 128, HALVES = HD / 64;
   constexpr int Q_BYTES = TA_ROWS * HD * 2, KV_BYTES = KEYS * HD * 2, RING = 3;
   constexpr int HALF_BYTES = 128 * 128, KB_BYTES = KEYS * 128;
@@ -671,6 +678,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     l_part[g * TA_ROWS + r] = m_mine == neg_inf ? 0.f : l * ex2((m_mine - m_fin) * scale_log2);
     asm volatile("bar.sync 1, 256;\n" ::: "memory");
     l = l_part[r] + l_part[TA_ROWS + r];
+    if (sink) l += ex2(-m_fin * scale_log2);                 // a key of score 0 that has no value
     // The last P V.  The phase before it on that barrier is P V (n - 3), which nothing so far has waited for: Q K^T
     // (n - 1) was issued after P V (n - 4) only, the phase before P V (n - 2) on the other barrier.  So that one first
     // (the group of the last tile waited for S (n - 1), and both groups have met since); the products end in order.
@@ -688,6 +696,11 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
         float o_acc[32];
         tc5::ld_32cols(tmem_o + t_row + g * OC + c0, o_acc);
         tc5::wait_ld();
+        if (gate && row_ok) {                                // the output times the sigmoid of the gate's pre-activation
+          const float* gr = gate + (int64_t)(tok0 + q0 + tk) * gate_stride + (int64_t)(head0 + hh) * HD + g * OC + c0;
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) o_acc[jj] = __fdividef(o_acc[jj], 1.f + __expf(-gr[jj]));
+        }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 pk;
@@ -722,7 +735,8 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
 template <int HD, int KT, bool TWO_GROUPS>
 int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride, const int* block_tables, int bt_stride,
               const int* cu_seqlens, const int* context_lens, const int* tiles, int num_tiles, int nh, int nkv, int gp,
-              int page_size, float scale, int window, int* err, cudaStream_t stream) {
+              int page_size, float scale, int window, int sink, const float* gate, int64_t gate_stride, int* err,
+              cudaStream_t stream) {
   const size_t smem = TWO_GROUPS ? (size_t)TA_ROWS * HD * 2 + 6 * (size_t)KT * HD * 2 + 1024
                                  : (size_t)TA_ROWS * HD * 2 + 4 * (size_t)KT * HD * 2 + 2 * (size_t)TA_ROWS * KT * 2 + 1024;
   auto kernel = TWO_GROUPS ? attn_prefill_tcgen05_two_groups_kernel<HD> : attn_prefill_tcgen05_kernel<HD, KT>;
@@ -738,7 +752,7 @@ int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_
   dim3 grid(nkv * (nh / nkv / gp), num_tiles);
   me_launch(kernel, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
             *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
-            context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, err);
+            context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, sink, gate, gate_stride, err);
   return 0;
 }
 
@@ -757,10 +771,13 @@ ME_API int me_attn_prefill_tcgen05_heads_per_block(int nh, int nkv, int hd, int 
 // q_map: the step's packed q|k|v rows as [tokens][row width], boxes (128 / heads-per-block) x 64; kv_map: the cache
 // slot as [pages * 2 * kv_heads * page_size][head_dim], boxes page_size x 64; both with the 128-byte swizzle.
 // ``tiles``: (request, first local query) per block, each covering 128 / heads-per-block query tokens.
+// ``sink``: the softmax's denominator has one more term, exp(0) (a key of score 0 without a value).  ``gate``: float32 rows of
+// nh * head_dim pre-activations (or null): the output is multiplied by their sigmoid.
 ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride,
                                    const int* block_tables, int bt_stride, const int* cu_seqlens, const int* context_lens,
                                    const int* tiles, int num_tiles, int nh, int nkv, int hd, int page_size, float scale,
-                                   int window, int key_tile, int* err, cudaStream_t stream) {
+                                   int window, int key_tile, int sink, const float* gate, int64_t gate_stride, int* err,
+                                   cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   const int gp = me_attn_prefill_tcgen05_heads_per_block(nh, nkv, hd, page_size);
   ME_REQUIRE(gp > 0, "me_attn_prefill_tcgen05: head_dim %d, %d/%d heads, pages of %d are not taken", hd, nh, nkv, page_size);
@@ -774,7 +791,7 @@ ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* 
              key_tile, page_size);
   int rc;
 #define ME_TA_ARGS q_map, kv_map, out, out_row_stride, block_tables, bt_stride, cu_seqlens, context_lens, tiles, num_tiles, nh, nkv, gp, \
-                   page_size, scale, window, err, stream
+                   page_size, scale, window, sink, gate, gate_stride, err, stream
   if (hd == 64) rc = key_tile == 64 ? launch_ta<64, 64, false>(ME_TA_ARGS) : launch_ta<64, 128, true>(ME_TA_ARGS);
   else rc = key_tile == 64 ? launch_ta<128, 64, false>(ME_TA_ARGS) : launch_ta<128, 128, true>(ME_TA_ARGS);
 #undef ME_TA_ARGS

@@ -5,8 +5,9 @@
 // u_t = proj_t + bias (zeros before a request's first token), y_t = sum_j w[:, j] * u_(t - taps + 1 + j), j < taps.
 // Channels are laid out q (nh x D) | k (nkv x D) | v (nkv x Dv); a mixer that takes its keys and values from another
 // layer has only q.  Of every q and k head the first ``rot`` elements are rotated, (2i, 2i+1) by the angle
-// position * inv_freq[i], formed in double precision and rounded once, to the float32 cosine and sine.  Cache rows hold
-// [key (D) | value (Dv)] per token and kv head: pool [pages][kv head][page offset][D + Dv].
+// position * inv_freq[i], formed in double precision and rounded once, to the float32 cosine and sine.  The cache is the
+// engine's usual one, [page][keys | values][kv head][page offset][HD] with HD >= max(D, Dv); a key fills the first D
+// elements of its row, a value the first Dv of its own.
 // The state [slots][taps-1][channels] (float32) holds u at the last taps-1 positions; it is read for positions before the
 // portion's first token and renewed by a second kernel.  No slot is read for positions below 0.
 #include "common.cuh"
@@ -40,7 +41,7 @@ conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __res
                     const int* __restrict__ positions, const int* __restrict__ token_req, const int* __restrict__ cu_seqlens,
                     const int* __restrict__ context_lens, const int* __restrict__ state_slots,
                     const int* __restrict__ slot_mapping, TO* __restrict__ q_out, TO* __restrict__ pool, int nh, int nkv, int D,
-                    int Dv, int page_size) {
+                    int Dv, int HD, int page_size) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -69,10 +70,10 @@ conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __res
   const int where = slot_mapping ? slot_mapping[t] : -1;
   if (where < 0) return;
   const int page = where / page_size, off = where - page * page_size;
-  int g, e;
-  if (c < Cq + Ck) { g = (c - Cq) / D; e = (c - Cq) - g * D; }
-  else { g = (c - Cq - Ck) / Dv; e = D + (c - Cq - Ck) - g * Dv; }
-  pool[(((int64_t)page * nkv + g) * page_size + off) * (D + Dv) + e] = from_f<TO>(y);
+  int g, e, which;
+  if (c < Cq + Ck) { which = 0; g = (c - Cq) / D; e = (c - Cq) - g * D; }
+  else { which = 1; g = (c - Cq - Ck) / Dv; e = (c - Cq - Ck) - g * Dv; }
+  pool[((((int64_t)page * 2 + which) * nkv + g) * page_size + off) * HD + e] = from_f<TO>(y);
 }
 
 __global__ void __launch_bounds__(256)
@@ -96,11 +97,11 @@ conv_state_kernel(ConvSrc s, float* __restrict__ state, const int* __restrict__ 
 
 // proj: [T, >= C] float32 with C = nh*D + (own_kv ? nkv*(D+Dv) : 0) leading channels q|k|v.  bias: [C] or null.  wt: [C, taps]
 // or null (no convolution; taps is then 1).  state: [slots, taps-1, C] float32 (unused for taps == 1).  inv_freq: [rot/2]
-// float64.  q_out: [T, nh*D]; pool: cache rows of out_dtype (unused without own_kv).
+// float64.  q_out: [T, nh*D]; pool: [pages][2][nkv][page_size][HD] of out_dtype (unused without own_kv).
 ME_API int me_conv_rope_kv(const float* proj, int64_t proj_stride, const float* bias, const float* wt, float* state, int taps,
                            const double* inv_freq, int rot, const int* positions, const int* token_req, const int* cu_seqlens,
                            const int* context_lens, const int* state_slots, const int* slot_mapping, void* q_out, void* pool,
-                           int out_dtype, int T, int B, int nh, int nkv, int D, int Dv, int own_kv, int page_size,
+                           int out_dtype, int T, int B, int nh, int nkv, int D, int Dv, int HD, int own_kv, int page_size,
                            cudaStream_t stream) {
   if (T == 0) return 0;
   ME_REQUIRE(T > 0 && B > 0 && nh > 0 && D > 0 && taps >= 1, "me_conv_rope_kv: bad sizes");
@@ -112,7 +113,7 @@ ME_API int me_conv_rope_kv(const float* proj, int64_t proj_stride, const float* 
   ME_DISPATCH_DTYPE(out_dtype, TO,
                     me_launch(conv_rope_kv_kernel<TO>, grid, dim3(threads), 0, stream, s, wt, inv_freq, rot, positions, token_req,
                               cu_seqlens, context_lens, state_slots, own_kv ? slot_mapping : (const int*)nullptr, (TO*)q_out,
-                              (TO*)pool, nh, own_kv ? nkv : 0, D, Dv, page_size));
+                              (TO*)pool, nh, own_kv ? nkv : 0, D, Dv, HD, page_size));
   ME_LAUNCH_CHECK("me_conv_rope_kv");
   if (taps > 1) {
     me_launch(conv_state_kernel, dim3(B, (s.C + threads - 1) / threads), dim3(threads), 0, stream, s, state, cu_seqlens,

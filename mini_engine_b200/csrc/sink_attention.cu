@@ -5,8 +5,9 @@
 //
 // A request's portion of q_len tokens ends at context length L: local query i sits at position p = L - q_len + i and
 // sees the cached keys j with j <= p and, with a window w, j > p - w.  Weights are exp(s_j) / (sink + sum exp(s_j)),
-// sink = 1 with the sink and 0 without: the running softmax simply starts from maximum 0 and sum 1.  Cache rows hold
-// [key (D) | value (Dv)] per token and kv head.  Key tiles start at multiples of SA_BK counted from position 0, so the
+// sink = 1 with the sink and 0 without: the running softmax simply starts from maximum 0 and sum 1.  The cache is the
+// engine's usual one, [page][keys | values][kv head][page offset][HD], with HD >= max(D, Dv): a key fills the first D
+// elements of its row, a value the first Dv of its own.  Key tiles start at multiples of SA_BK counted from position 0, so the
 // order of a query's sums does not depend on how the prompt was cut or on what shares the batch.
 //
 // One block = 16 queries of one request x one query head; 128 threads; thread (r, c) owns row r = tid / 8, keys
@@ -20,7 +21,7 @@ __global__ void __launch_bounds__(SA_THREADS)
 sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restrict__ gate, int64_t gate_stride,
                  T* __restrict__ out, int64_t out_stride, const T* __restrict__ pool, const int* __restrict__ block_tables,
                  int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
-                 const int* __restrict__ tiles, int nh, int nkv, int D, int Dv, int page_size, float scale, int window,
+                 const int* __restrict__ tiles, int nh, int nkv, int D, int Dv, int HD, int page_size, float scale, int window,
                  int sink) {
   extern __shared__ float smem[];
   pdl_wait();
@@ -38,6 +39,7 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
   const int rows = min(SA_BQ, q_len - q0);
   const int* bt = block_tables + (int64_t)b * bt_stride;
   const int row_len = D + Dv;
+  const int64_t plane = (int64_t)nkv * page_size * HD;       // from a page's keys to its values
 
   for (int idx = tid; idx < SA_BQ * D; idx += SA_THREADS) {
     const int rr = idx / D, d = idx - rr * D;
@@ -62,7 +64,10 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
       float v = 0.f;
       if (j < hi) {
         const int page = bt[j / page_size];
-        if (page >= 0) v = to_f<T>(pool[(((int64_t)page * nkv + kvh) * page_size + (j % page_size)) * row_len + d]);
+        if (page >= 0) {
+          const int64_t at = (((int64_t)page * 2 * nkv + kvh) * page_size + (j % page_size)) * HD;
+          v = to_f<T>(d < D ? pool[at + d] : pool[at + plane + d - D]);
+        }
       }
       if (d < D) Ks[jj * ldk + d] = v;
       else Vs[jj * ldv + d - D] = v;
@@ -129,14 +134,15 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
 
 ME_API int me_sink_attn_tile_q() { return SA_BQ; }
 
-// q: [T, nh*D]; gate: float32 [T, >= nh*Dv] pre-activations or null; out: [T, nh*Dv]; pool: cache rows [D | Dv].
+// q: [T, nh*D]; gate: float32 [T, >= nh*Dv] pre-activations or null; out: [T, nh*Dv]; pool: [pages][2][nkv][page_size][HD].
 // tiles: [num_tiles, 2] (request, first local query) for requests that bring several tokens; the first num_decodes
 // requests bring one token each and get one block per head.
 ME_API int me_sink_attn(const void* q, int dtype, int64_t q_stride, const float* gate, int64_t gate_stride, void* out,
                         int64_t out_stride, const void* pool, const int* block_tables, int bt_stride, const int* cu_seqlens,
                         const int* context_lens, const int* tiles, int num_tiles, int num_decodes, int nh, int nkv, int D, int Dv,
-                        int page_size, float scale, int window, int sink, cudaStream_t stream) {
+                        int HD, int page_size, float scale, int window, int sink, cudaStream_t stream) {
   ME_REQUIRE(D >= 1 && D <= SA_MAX && Dv >= 1 && Dv <= SA_MAX, "me_sink_attn: key size %d / value size %d beyond %d", D, Dv, SA_MAX);
+  ME_REQUIRE(HD >= D && HD >= Dv, "me_sink_attn: cache rows of %d elements are too short", HD);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh <= 65535, "me_sink_attn: %d heads, %d kv heads", nh, nkv);
   const size_t smem = sizeof(float) * ((size_t)(SA_BQ + SA_BK) * (D + 1) + (size_t)SA_BK * (Dv + 1) + SA_BQ * (SA_BK + 1));
   ME_DISPATCH_DTYPE(dtype, T, {
@@ -149,11 +155,11 @@ ME_API int me_sink_attn(const void* q, int dtype, int64_t q_stride, const float*
     if (num_decodes > 0)
       me_launch(sink_attn_kernel<T>, dim3(num_decodes, nh), dim3(SA_THREADS), smem, stream, (const T*)q, q_stride, gate, gate_stride,
                 (T*)out, out_stride, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, (const int*)nullptr, nh, nkv,
-                D, Dv, page_size, scale, window, sink);
+                D, Dv, HD, page_size, scale, window, sink);
     if (num_tiles > 0)
       me_launch(sink_attn_kernel<T>, dim3(num_tiles, nh), dim3(SA_THREADS), smem, stream, (const T*)q, q_stride, gate, gate_stride,
                 (T*)out, out_stride, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles, nh, nkv, D, Dv,
-                page_size, scale, window, sink);
+                HD, page_size, scale, window, sink);
   });
   ME_LAUNCH_CHECK("me_sink_attn");
   return 0;

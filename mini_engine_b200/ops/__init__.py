@@ -39,7 +39,7 @@ _PROTOS = {
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _P],
+    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _I, _P, _L, _P],
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _I, _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _P],
@@ -47,15 +47,15 @@ _PROTOS = {
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _P, _P],
     "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
     "me_gemm_tcgen05_shared": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
-    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
+    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _L, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
     "me_test_wait_expires": [_P, _I, _P, _P],
     "me_sandwich_norm": [_P, _P, _I, _P, _F, _P, _F, _P, _I, _P, _I, _I, _I, _P],
     "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P],
-    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
@@ -821,9 +821,11 @@ def prefill_tcgen05_heads_per_block(num_heads: int, num_kv_heads: int, head_dim:
 
 
 def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
-                              scale, window, tiles=None, num_tiles=None, key_tile: int = 0) -> None:
+                              scale, window, tiles=None, num_tiles=None, key_tile: int = 0, sink: bool = False,
+                              gate: Optional[torch.Tensor] = None) -> None:
     """The tcgen05 / tensor-memory prefill kernel (bfloat16, head_dim 64 or 128, page sizes dividing 128) over
-    tiles of 128 / heads-per-block tokens; Q, K and V arrive by tensor-map loads."""
+    tiles of 128 / heads-per-block tokens; Q, K and V arrive by tensor-map loads.  ``sink``: one more term, exp(0), in
+    the softmax's denominator; ``gate``: float32 rows of pre-activations whose sigmoid multiplies the output."""
     gp = prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, head_dim, page_size)
     _need(gp > 0 and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.data_ptr() % 16 == 0,
           "attention_prefill_tcgen05: shape or dtype not taken by the kernel")
@@ -833,15 +835,18 @@ def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool,
     _call("me_attn_prefill_tcgen05", matrix_tensor_map(qkv, tq).ptr, kv_tensor_map(pool, page_size).ptr, out.data_ptr(),
           out.stride(0), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), tiles.data_ptr(), num_tiles, num_heads, num_kv_heads, head_dim, page_size,
-          float(scale), int(window or 0), key_tile, meta.error_flag.data_ptr(), _stream())
+          float(scale), int(window or 0), key_tile, 1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
+          meta.error_flag.data_ptr(), _stream())
 
 
 use_tcgen05_attention = True   # False: portions of prompts use the mma.sync kernel instead (a switch for comparisons)
 
 
 def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
-                     scale, window, kind: str = "auto") -> None:
-    """The split-K decode kernel and its merge over requests [0, meta.num_decodes).
+                     scale, window, kind: str = "auto", sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
+    """The split-K decode kernel and its merge over requests [0, meta.num_decodes).  ``sink``: one more term, exp(0), in
+    the softmax's denominator (added once, in the merge); ``gate``: float32 rows of pre-activations whose sigmoid
+    multiplies the output.
 
     ``kind`` picks the partition kernel: "auto" (for bfloat16 with head_dim 64 or 128 the tensor cores, fed by
     tensor-map loads where the page size divides 128, else by cp.async; otherwise the CUDA cores), or one
@@ -856,7 +861,8 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
           pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), D, num_heads, num_kv_heads, head_dim, page_size, float(scale),
           int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts,
-          _ptr(meta.error_flag), DECODE_KINDS[kind], tm.ptr if tm is not None else 0, _stream())
+          _ptr(meta.error_flag), DECODE_KINDS[kind], tm.ptr if tm is not None else 0, 1 if sink else 0, _ptr(gate),
+          gate.stride(0) if gate is not None else 0, _stream())
     global launches
     launches += 1          # partition kernel + merge kernel
 
@@ -1222,14 +1228,15 @@ def conv_rope_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_weight: 
     _need(inv_freq.dtype == torch.float64 and inv_freq.numel() * 2 == rot_dims, "conv_rope_kv: inv_freq must be float64 [rot_dims / 2]")
     _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, num_heads * dim), "conv_rope_kv: query output shape")
     if own_kv:
-        _need(pool is not None and pool.is_contiguous() and pool.shape[-1] == dim + vdim and pool.dtype == q_out.dtype
-              and slot_mapping is not None, "conv_rope_kv: cache rows must hold dim + vdim values of the activations' dtype")
+        _need(pool is not None and pool.is_contiguous() and pool.dim() == 5 and pool.shape[1] == 2 and pool.shape[-1] >= max(dim, vdim)
+              and pool.dtype == q_out.dtype and slot_mapping is not None,
+              "conv_rope_kv: the cache must be [pages, 2, kv heads, page, >= max(dim, vdim)] of the activations' dtype")
     meta = ctx.attn_meta
     _call("me_conv_rope_kv", proj.data_ptr(), proj.stride(0), _ptr(bias), _ptr(conv_weight), _ptr(state) if taps > 1 else 0, taps,
           inv_freq.data_ptr(), rot_dims, ctx.positions.data_ptr(), ctx.token_req.data_ptr(), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), ctx.state_slots.data_ptr(), _ptr(slot_mapping) if own_kv else 0, q_out.data_ptr(),
-          _ptr(pool) if own_kv else 0, _dt(q_out), T, meta.num_reqs, num_heads, num_kv_heads, dim, vdim, 1 if own_kv else 0,
-          page_size, _stream())
+          _ptr(pool) if own_kv else 0, _dt(q_out), T, meta.num_reqs, num_heads, num_kv_heads, dim, vdim,
+          pool.shape[-1] if own_kv else 0, 1 if own_kv else 0, page_size, _stream())
 
 
 use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor cores where the sizes allow; a switch for comparisons
@@ -1238,21 +1245,40 @@ use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor
 def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, pool: torch.Tensor, page_size: int,
                    block_tables: torch.Tensor, meta, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
                    window: Optional[int], sink: bool) -> None:
-    """Attention over cache rows [key (dim) | value (vdim)]: ``q`` [T, heads * dim] -> ``out`` [T, heads * vdim]; a query at
-    position p sees keys p - window < j <= p; with ``sink`` the softmax's denominator has one more term, exp(0); ``gate``
-    (float32 rows of pre-activations, heads * vdim wide) multiplies the output by its sigmoid."""
+    """Attention over the paged cache with keys of ``dim`` and values of ``vdim`` elements: ``q`` [T, heads * dim] -> ``out``
+    [T, heads * vdim]; a query at position p sees keys p - window < j <= p; with ``sink`` the softmax's denominator has one
+    more term, exp(0); ``gate`` (float32 rows of pre-activations, heads * vdim wide) multiplies the output by its sigmoid.
+
+    bfloat16 with keys and values of 64 or 128 elements (the cache row's size) runs the engine's tensor-core kernels, the
+    tcgen05 one for portions of prompts and the split-K one for single tokens; everything else the CUDA-core kernel of
+    csrc/sink_attention.cu."""
     T = q.shape[0]
+    HD = pool.shape[-1]
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * dim and tuple(out.shape) == (T, num_heads * vdim),
           "sink_attention: shapes")
-    _need(pool.dtype == q.dtype == out.dtype and pool.is_contiguous() and pool.shape[-1] == dim + vdim, "sink_attention: cache rows")
+    _need(pool.dtype == q.dtype == out.dtype and pool.is_contiguous() and pool.dim() == 5 and pool.shape[1] == 2 and HD >= max(dim, vdim),
+          "sink_attention: the cache must be [pages, 2, kv heads, page, >= max(dim, vdim)] of the activations' dtype")
     _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] == num_heads * vdim),
           "sink_attention: the gate must be float32 rows")
     _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "sink_attention: block tables")
+    decodes, tiles_left = meta.num_decodes, True
+    fast = (use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
+            and meta.error_flag is not None and q.is_contiguous() and q.data_ptr() % 16 == 0)
+    if fast and decodes:
+        attention_decode(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window, sink=sink, gate=gate)
+        decodes = 0
+    if fast and meta.num_tiles > 0 and use_tcgen05_attention and prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, HD, page_size) > 0:
+        attention_prefill_tcgen05(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window,
+                                  sink=sink, gate=gate)
+        tiles_left = False
     tiles, n_tiles = meta.tile_lists[SINK_ATTN_TILE_Q]
-    _call("me_sink_attn", q.data_ptr(), _dt(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
-          out.stride(0), pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
-          meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles, meta.num_decodes, num_heads, num_kv_heads, dim, vdim, page_size,
-          float(scale), int(window or 0), 1 if sink else 0, _stream())
+    if not tiles_left:
+        n_tiles = 0
+    if decodes or n_tiles:
+        _call("me_sink_attn", q.data_ptr(), _dt(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
+              out.stride(0), pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
+              meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles, decodes, num_heads, num_kv_heads, dim, vdim, HD, page_size,
+              float(scale), int(window or 0), 1 if sink else 0, _stream())
 
 
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, weights: torch.Tensor) -> None:

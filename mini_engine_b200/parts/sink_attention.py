@@ -6,7 +6,8 @@ a request are its state); rotary positions on neighbouring pairs of the first ``
 head; score = q . k * scale; a query at position p sees keys p - window < j <= p (all j <= p without a window); the
 weights are exp(s_j) / (sink + sum exp(s_j)) with sink = 1 when ``sink`` is set (a key of score 0 that has no value);
 the concatenated heads are multiplied by sigmoid(W_g h) when ``gate`` is set; then the output projection.  Keys have
-``dim`` elements and values ``vdim``; a cache row holds [key | value] of one token and kv head.
+``dim`` elements and values ``vdim``; the cache is the engine's usual one (pages of keys and of values) with rows of
+max(dim, vdim) elements, so that equal sizes of 64 or 128 run the engine's tensor-core attention kernels.
 
 ``own_kv`` False: the mixer has no key and value projections; it reads the cache rows of another call (``call.kv_slot``)
 with its own queries, window and everything else.  ``cache_window``: what the cache must keep for all mixers that read
@@ -78,7 +79,7 @@ class SinkAttention(Mixer):
         return decls
 
     def cache_needs(self):
-        needs = [KVCacheNeed(self.num_kv_heads, self.dim + self.vdim, self.cache_window, planes=1)] if self.own_kv else []
+        needs = [KVCacheNeed(self.num_kv_heads, max(self.dim, self.vdim), self.cache_window)] if self.own_kv else []
         if self.taps > 1:
             needs.append(StateNeed((self.taps - 1, self.channels), "float32", "conv"))
         return needs

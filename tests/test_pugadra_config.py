@@ -38,7 +38,7 @@ def test_every_number_comes_from_the_file():
 def test_cache_groups_keep_the_widest_window_of_their_readers():
     _, model = build_model_from_config_dict(zoo.C)
     groups, location, states = plan_cache_groups(model)
-    assert [(g.window, g.num_kv_heads, g.head_dim, g.planes) for g in groups] == [(128, 2, 128, 1), (None, 4, 96, 1)]
+    assert [(g.window, g.num_kv_heads, g.head_dim, g.planes) for g in groups] == [(128, 2, 64, 2), (None, 4, 64, 2)]
     assert sorted(location) == [0, 2]                       # the layer that borrows keys has no pages of its own
     assert states[1] == [StateNeed((2, 8 * 64), "float32", "conv")]        # ... and a state for its queries only
     assert states[0] == [StateNeed((2, 8 * 64 + 2 * 128), "float32", "conv")]

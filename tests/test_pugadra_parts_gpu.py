@@ -98,9 +98,10 @@ def test_projections_through_convolution_and_rotation_in_portions_with_slots_use
         ref_q.append(plain.rotate_pairs(y[:, :H * D].reshape(-1, H, D), pos, base, rot))
         if own_kv:
             k = plain.rotate_pairs(y[:, H * D:H * D + G * D].reshape(-1, G, D), pos, base, rot)
-            ref_kv.append(torch.cat((k, y[:, H * D + G * D:].reshape(-1, G, V)), dim=2))
+            ref_kv.append((k, y[:, H * D + G * D:].reshape(-1, G, V)))
     state = torch.full((slots, max(taps - 1, 1), C), float("nan"), device=DEV)[:, :max(taps - 1, 0)].contiguous()
-    pool = torch.full((pages, 1, G, ps, D + V), float("nan"), device=DEV)
+    HD = max(D, V) + 3                                        # cache rows may be longer than a key or a value
+    pool = torch.full((pages, 2, G, ps, HD), float("nan"), device=DEV)
     perm = torch.randperm(pages, generator=g(3)).tolist()
     tables = [perm[0:3], perm[3:5], perm[5:9]]
     slot_of = [2, 0, 2]                                     # request 2 takes request 0's slot once that has ended
@@ -127,25 +128,28 @@ def test_projections_through_convolution_and_rotation_in_portions_with_slots_use
         n = pos[r]
         assert torch.allclose(torch.cat(got[r]).double().view(n, H, D), ref_q[r][:n], atol=2e-5), f"queries of request {r}"
         if own_kv and r != 0:                               # (request 0 ended; nothing reused its pages here)
-            rows = torch.stack([pool[tables[r][j // ps], 0, :, j % ps] for j in range(n)]).cpu().double()
-            assert torch.allclose(rows, ref_kv[r][:n], atol=2e-5), f"cache rows of request {r}"
+            rows = torch.stack([pool[tables[r][j // ps], :, :, j % ps] for j in range(n)]).cpu().double()     # [n, 2, G, HD]
+            assert torch.allclose(rows[:, 0, :, :D], ref_kv[r][0][:n], atol=2e-5), f"cached keys of request {r}"
+            assert torch.allclose(rows[:, 1, :, :V], ref_kv[r][1][:n], atol=2e-5), f"cached values of request {r}"
+            assert torch.isnan(rows[:, 0, :, D:]).all() and torch.isnan(rows[:, 1, :, V:]).all()
 
 
 # ---- attention with a window, a sink and a gate ---------------------------------------------------------------
-def _paged(keys_values, ps, dtype, seed):
-    """Cache rows [key | value] of several requests in pages handed out in a shuffled order."""
-    need = [(kv.shape[0] + ps - 1) // ps for kv in keys_values]
+def _paged(keys, values, ps, dtype, seed):
+    """The keys and values of several requests in pages handed out in a shuffled order: [pages, 2, kv heads, page, row]."""
+    need = [(k.shape[0] + ps - 1) // ps for k in keys]
     pages = sum(need) + 3
-    G, R = keys_values[0].shape[1:]
-    pool = torch.full((pages, 1, G, ps, R), float("nan"), dtype=dtype, device=DEV)
+    G, D, V = keys[0].shape[1], keys[0].shape[2], values[0].shape[2]
+    pool = torch.full((pages, 2, G, ps, max(D, V)), float("nan"), dtype=dtype, device=DEV)
     perm = torch.randperm(pages, generator=g(seed)).tolist()
-    bt = torch.full((len(keys_values), max(need)), -1, dtype=torch.int32)
-    for b, kv in enumerate(keys_values):
+    bt = torch.full((len(keys), max(need)), -1, dtype=torch.int32)
+    for b, (k, v) in enumerate(zip(keys, values)):
         for i in range(need[b]):
             page = perm.pop()
             bt[b, i] = page
-            chunk = kv[i * ps:(i + 1) * ps]
-            pool[page, 0, :, :chunk.shape[0]] = chunk.transpose(0, 1).to(dtype).to(DEV)
+            n = k[i * ps:(i + 1) * ps].shape[0]
+            pool[page, 0, :, :n, :D] = k[i * ps:(i + 1) * ps].transpose(0, 1).to(dtype).to(DEV)
+            pool[page, 1, :, :n, :V] = v[i * ps:(i + 1) * ps].transpose(0, 1).to(dtype).to(DEV)
     return pool, bt.to(DEV)
 
 
@@ -160,12 +164,14 @@ def _attention_case(ops, dtype, H, G, D, V, window, sink, ps, lens, contexts, se
     if boost:
         boost(qs, ks)
     qs, ks, vs = ([t.to(dt).float() for t in ts] for ts in (qs, ks, vs))       # what the kernel is given, exactly
-    pool, bt = _paged([torch.cat((k, v), dim=2) for k, v in zip(ks, vs)], ps, dt, seed)
+    pool, bt = _paged(ks, vs, ps, dt, seed)
     meta, _, _ = _meta(list(lens), list(contexts))
+    meta.error_flag = torch.zeros(4, dtype=torch.int32, device=DEV)
     q = torch.cat([qq[c - n:].reshape(n, H * D) for qq, n, c in zip(qs, lens, contexts)]).to(dt).to(DEV)
     gate_rows = torch.cat([gg[c - n:] for gg, n, c in zip(gs, lens, contexts)]).to(DEV) if gate else None
     out = torch.empty(q.shape[0], H * V, dtype=dt, device=DEV)
     ops.sink_attention(q, gate_rows, out, pool, ps, bt, meta, H, G, D, V, scale, window, sink)
+    assert not meta.error_flag.any()
     res, o = [], 0
     for qq, kk, vv, gg, n, c in zip(qs, ks, vs, gs, lens, contexts):
         ref = _plain_attention(qq.double(), kk.double(), vv.double(), scale, window, sink)[c - n:].reshape(n, H * V)
