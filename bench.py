@@ -728,7 +728,7 @@ def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
     that their summed time makes: bytes for the element-wise kernels, multiply-adds for attention and the experts."""
     W = cfg["width"]
     side = cfg.get("token_side", {}).get("dim", 0)
-    need = {k: 0.0 for k in ("me_sandwich_norm", "me_conv_rope_kv", "me_sink_attn", "me_sink_attn_mma", "me_clamped_glu", "me_moe_gemm",
+    need = {k: 0.0 for k in ("me_sandwich_norm", "me_conv_rope_kv", "me_sink_attn", "me_attn_prefill_tcgen05", "me_clamped_glu", "me_moe_gemm",
                              "me_moe_combine", "me_token_side_gate")}
     for layer in cfg["layers"]:
         m, mlp = layer["mixer"], layer["mlp"]
@@ -740,7 +740,7 @@ def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
         need["me_conv_rope_kv"] += T * C * (4 + item)
         att = 2.0 * H * (D + V) * _window_pairs(T, m.get("mask", {}).get("size"))
         need["me_sink_attn"] += att
-        need["me_sink_attn_mma"] += att
+        need["me_attn_prefill_tcgen05"] += att
         if mlp is not None and mlp["kind"] == "dense":
             need["me_clamped_glu"] += T * mlp["ff"] * 3 * item
         elif mlp is not None:
@@ -750,7 +750,7 @@ def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
                 need["me_clamped_glu"] += T * mlp["shared"]["ff"] * 3 * item
         if side:
             need["me_token_side_gate"] += T * side * (4 + 2 * item)
-    return _fractions(need, ("me_sink_attn", "me_sink_attn_mma", "me_moe_gemm"), times, pk)
+    return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_moe_gemm"), times, pk)
 
 
 def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:

@@ -5,7 +5,8 @@
 // u_t = proj_t + bias (zeros before a request's first token), y_t = sum_j w[:, j] * u_(t - taps + 1 + j), j < taps.
 // Channels are laid out q (nh x D) | k (nkv x D) | v (nkv x Dv); a mixer that takes its keys and values from another
 // layer has only q.  Of every q and k head the first ``rot`` elements are rotated, (2i, 2i+1) by the angle
-// position * inv_freq[i], formed in double precision and rounded once, to the float32 cosine and sine.  The cache is the
+// position * inv_freq[i]: the angle is formed in double precision and brought into [-pi, pi] there, so that the float32
+// sine and cosine are as exact at position 100,000 as at position 1.  The cache is the
 // engine's usual one, [page][keys | values][kv head][page offset][HD] with HD >= max(D, Dv); a key fills the first D
 // elements of its row, a value the first Dv of its own.
 // The state [slots][taps-1][channels] (float32) holds u at the last taps-1 positions; it is read for positions before the
@@ -35,6 +36,23 @@ __device__ __forceinline__ float conv_output(const ConvSrc& s, const float* __re
   return acc;
 }
 
+// Where channel c of token t goes: a query element, or (through the slot mapping) an element of a cached key or value.
+template <typename TO>
+__device__ __forceinline__ void conv_store(float y, int c, int t, int where, TO* __restrict__ q_out, TO* __restrict__ pool, int Cq,
+                                           int Ck, int nkv, int D, int Dv, int HD, int page_size) {
+  if (c < Cq) {
+    q_out[(int64_t)t * Cq + c] = from_f<TO>(y);
+    return;
+  }
+  if (where < 0) return;
+  const int page = where / page_size, off = where - page * page_size;
+  int g, e, which;
+  if (c < Cq + Ck) { which = 0; g = (c - Cq) / D; e = (c - Cq) - g * D; }
+  else { which = 1; g = (c - Cq - Ck) / Dv; e = (c - Cq - Ck) - g * Dv; }
+  pool[((((int64_t)page * 2 + which) * nkv + g) * page_size + off) * HD + e] = from_f<TO>(y);
+}
+
+// A thread owns two neighbouring channels (2i, 2i+1): with an even head size they are a rotated pair or no part of one.
 template <typename TO>
 __global__ void __launch_bounds__(256)
 conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __restrict__ inv_freq, int rot,
@@ -45,35 +63,33 @@ conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __res
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
   if (c >= s.C) return;
+  const bool two = c + 1 < s.C;
   const int b = token_req[t];
   const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
   const int start = context_lens[b] - q_len;
   const int i = t - tok0;
   const int slot = state_slots[b];
   const int Cq = nh * D, Ck = nkv * D;
-  float y = conv_output(s, wt, tok0, i, start, slot, c);
-  int d = -1;                                   // index inside a rotated head, if this channel belongs to one
-  if (c < Cq + Ck) d = (c < Cq ? c : c - Cq) % D;
-  if (d >= 0 && d < rot) {
-    const float other = conv_output(s, wt, tok0, i, start, slot, c ^ 1);   // D and rot are even: the pair shares a head
-    double sn, cs;
-    sincos((double)positions[t] * inv_freq[d >> 1], &sn, &cs);
-    const float fc = (float)cs, fs = (float)sn;
-    y = (d & 1) ? fmaf(y, fc, other * fs) : fmaf(y, fc, -other * fs);
-  }
-  if (c < Cq) {
-    q_out[(int64_t)t * Cq + c] = from_f<TO>(y);
-    return;
+  float y0 = conv_output(s, wt, tok0, i, start, slot, c);
+  float y1 = two ? conv_output(s, wt, tok0, i, start, slot, c + 1) : 0.f;
+  if (rot > 0 && c < Cq + Ck) {
+    const int d = (c < Cq ? c : c - Cq) % D;        // even, since D is even when anything is rotated
+    if (d < rot) {
+      // the angle in double precision, brought into [-pi, pi] there, then the float32 sine and cosine of that
+      double ang = (double)positions[t] * inv_freq[d >> 1];
+      ang -= 6.283185307179586476925 * rint(ang * 0.15915494309189533577);
+      float sn, cs;
+      sincosf((float)ang, &sn, &cs);
+      const float u = y0, v = y1;
+      y0 = fmaf(u, cs, -v * sn);
+      y1 = fmaf(v, cs, u * sn);
+    }
   }
   const int where = slot_mapping ? slot_mapping[t] : -1;
-  if (where < 0) return;
-  const int page = where / page_size, off = where - page * page_size;
-  int g, e, which;
-  if (c < Cq + Ck) { which = 0; g = (c - Cq) / D; e = (c - Cq) - g * D; }
-  else { which = 1; g = (c - Cq - Ck) / Dv; e = (c - Cq - Ck) - g * Dv; }
-  pool[((((int64_t)page * 2 + which) * nkv + g) * page_size + off) * HD + e] = from_f<TO>(y);
+  conv_store<TO>(y0, c, t, where, q_out, pool, Cq, Ck, nkv, D, Dv, HD, page_size);
+  if (two) conv_store<TO>(y1, c + 1, t, where, q_out, pool, Cq, Ck, nkv, D, Dv, HD, page_size);
 }
 
 __global__ void __launch_bounds__(256)
@@ -109,7 +125,7 @@ ME_API int me_conv_rope_kv(const float* proj, int64_t proj_stride, const float* 
   ME_REQUIRE(taps == 1 || (state != nullptr && wt != nullptr), "me_conv_rope_kv: %d taps need weights and a state", taps);
   ConvSrc s{proj, proj_stride, bias, state, nh * D + (own_kv ? nkv * (D + Dv) : 0), taps};
   const int threads = s.C >= 256 ? 256 : 64;
-  dim3 grid(T, (s.C + threads - 1) / threads);
+  dim3 grid(T, ((s.C + 1) / 2 + threads - 1) / threads);
   ME_DISPATCH_DTYPE(out_dtype, TO,
                     me_launch(conv_rope_kv_kernel<TO>, grid, dim3(threads), 0, stream, s, wt, inv_freq, rot, positions, token_req,
                               cu_seqlens, context_lens, state_slots, own_kv ? slot_mapping : (const int*)nullptr, (TO*)q_out,
