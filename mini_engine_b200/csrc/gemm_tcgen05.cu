@@ -52,13 +52,22 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], in
 // writes four rows' 128 bytes.  Without 16-byte alignment of the rows of C (``vec`` false) they leave one by one.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
+// EPI 2: g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: as they are), g * sigmoid(alpha * g) * (u + 1).
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+}
+
 template <int EPI, typename TO, int OUT_COLS, typename Load, typename Fix>
 __device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char* stage, TO* __restrict__ C, int64_t ldc, int M, int N,
-                                           int m0, int n0, int lane_base, int lane, bool vec) {
+                                           int m0, int n0, int lane_base, int lane, bool vec, float limit = 0.f, float alpha = 1.f) {
   const int m = m0 + lane_base + lane;
   // 32 results of the lane's row from output column ``c`` on
   auto results = [&](int c, float (&g)[32]) {
-    if (EPI == 1) {
+    if (EPI == 1 || EPI == 2) {
       float u[32];
       load(c, g);
       load(OUT_COLS + c, u);
@@ -66,7 +75,7 @@ __device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char
       fix(c, g);
       fix(OUT_COLS + c, u);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) g[j] = silu_mul(g[j], u[j]);
+      for (int j = 0; j < 32; ++j) g[j] = EPI == 1 ? silu_mul(g[j], u[j]) : clamped_glu(g[j], u[j], limit, alpha);
     } else {
       load(c, g);
       tc5::wait_ld();
@@ -252,6 +261,123 @@ int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M,
   dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TG_BM - 1) / TG_BM, (num_kb + kb_per_split - 1) / kb_per_split);
   me_launch(gemm_tcgen05_kernel<BN, EPI, TO, DEEP>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
             *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, kb_per_split, split_stride, err);
+  return 0;
+}
+
+// ---- one product per expert (a routed feed-forward) ------------------------------------------------------------
+// The rows of A lie in expert order: expert e owns rows [offsets[e], offsets[e + 1]), numbers that exist on the device only.
+// W is [E][rows_w][K]; with EPI 2 an expert's rows are gate rows then up rows and the result is the clamped gated
+// activation.  The grid has a row tile to spare per expert; a block walks the offsets to find its expert and its rows and
+// leaves if there are none.  A tile's box of A may reach into the next expert's rows and its box of W into the next
+// expert's weights: those results are never stored.  Everything else is the kernel above.
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(TG_THREADS)
+gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                            TO* __restrict__ C, int64_t ldc, const int* __restrict__ offsets, int E, int N, int rows_w, int K,
+                            float limit, float alpha, int* __restrict__ err) {
+  constexpr int STAGES = tg_stages<BN>(false);
+  constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
+  constexpr int OUT_COLS = EPI == 2 ? BN / 2 : BN;
+  extern __shared__ unsigned char tg_smem_raw[];
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+  __shared__ uint32_t tmem_slot;
+  unsigned char* smem = tg_smem_raw + ((1024u - (tma::smem_addr(tg_smem_raw) & 1023u)) & 1023u);
+  const int warp = tc5::uniform_warp_index(), lane = threadIdx.x & 31;
+  pdl_wait();                                      // the offsets and A are written by kernels of this step
+  int tile = blockIdx.y, e = 0, m0 = 0, m_end = 0;
+  for (; e < E; ++e) {
+    const int lo = offsets[e], n = offsets[e + 1] - lo, tiles = (n + TG_BM - 1) / TG_BM;
+    if (tile < tiles) { m0 = lo + tile * TG_BM; m_end = lo + n; break; }
+    tile -= tiles;
+  }
+  if (e == E) return;                              // (the whole block: nothing is allocated yet)
+  const int n0 = blockIdx.x * OUT_COLS, w0 = e * rows_w;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tma::mbar_init(&full_bar[s], 1);
+      tma::mbar_init(&empty_bar[s], 1);
+    }
+    tma::mbar_init(&done_bar, 1);
+    tma::mbar_fence_init();
+    tma::prefetch_map(&map_a);
+    tma::prefetch_map(&map_w);
+  }
+  if (warp == 1) tc5::tmem_alloc(&tmem_slot, BN < 32 ? 32 : BN);
+  tc5::fence_before_sync();
+  __syncthreads();
+  tc5::fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = tma::mbar_wait(&empty_bar[s], ((kb / STAGES) & 1) ^ 1);
+        if (!ok) break;
+        unsigned char* a_dst = smem + s * STAGE_BYTES;
+        unsigned char* b_dst = a_dst + TG_A_BYTES;
+        tma::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        if (EPI == 2) {
+          tma::load_2d(b_dst, &map_w, kb * TG_BK, w0 + n0, &full_bar[s]);
+          tma::load_2d(b_dst + B_BYTES / 2, &map_w, kb * TG_BK, w0 + N + n0, &full_bar[s]);
+        } else {
+          tma::load_2d(b_dst, &map_w, kb * TG_BK, w0 + n0, &full_bar[s]);
+        }
+        tma::load_2d(a_dst, &map_a, kb * TG_BK, m0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc = tc5::instr_desc_bf16(TG_BM, BN);
+    const tc5::DescWords a_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem));
+    const tc5::DescWords b_desc = tc5::words_of(tc5::smem_desc_k_major_sw128(smem + TG_A_BYTES));
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % STAGES;
+      ok = tc5::mbar_wait_warp(&full_bar[s], (kb / STAGES) & 1);
+      if (!ok) break;
+      tc5::fence_after_sync();
+      const uint32_t stage = (uint32_t)(s * STAGE_BYTES) >> 4;
+#pragma unroll
+      for (int k = 0; k < TG_BK / 16; ++k)
+        tc5::mma_f16_elect(tmem, a_desc, stage + 2 * k, b_desc, stage + 2 * k, idesc, kb > 0 || k > 0);
+      tc5::commit_elect(&empty_bar[s]);
+    }
+    tc5::commit_elect(&done_bar);
+  } else {
+    ok = tma::mbar_wait(&done_bar, 0);
+    tc5::fence_after_sync();
+    const int lane_base = (warp & 3) * 32;
+    const bool vec = (ldc * sizeof(TO)) % 16 == 0 && (n0 * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
+    if (ok) {
+      auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + col, v); };
+      auto fix = [](int, float (&)[32]) {};
+      write_rows<EPI, TO, OUT_COLS>(load, fix, smem + (warp & 3) * 4096, C, ldc, m_end, N, m0, n0, lane_base, lane, vec, limit, alpha);
+    }
+  }
+  if (!ok) atomicOr(err + 1, 1);
+  pdl_launch_dependents();
+  tc5::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tc5::tmem_dealloc(tmem, BN < 32 ? 32 : BN);
+}
+
+template <int BN, int EPI, typename TO>
+int launch_grouped(const void* map_a, const void* map_w, void* C, int64_t ldc, const int* offsets, int E, int rows, int N, int rows_w,
+                   int K, float limit, float alpha, int* err, cudaStream_t stream) {
+  constexpr int STAGES = tg_stages<BN>(false);
+  const size_t smem = (size_t)STAGES * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_grouped_kernel<BN, EPI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ME_REQUIRE(e == cudaSuccess, "me_gemm_tcgen05_grouped: cannot raise shared memory: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  constexpr int OUT_COLS = EPI == 2 ? BN / 2 : BN;
+  dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (rows + TG_BM - 1) / TG_BM + E);
+  me_launch(gemm_tcgen05_grouped_kernel<BN, EPI, TO>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
+            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, offsets, E, N, rows_w, K, limit, alpha, err);
   return 0;
 }
 
@@ -800,5 +926,25 @@ ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_
 #undef ME_TG_CASE
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_gemm_tcgen05");
+  return 0;
+}
+
+// One product per expert over rows in expert order (see gemm_tcgen05_grouped_kernel).  map_a: A [rows, K], boxes 128 x 64;
+// map_w: W as [E * rows_w, K], boxes 128 x 64 (glu: 64 x 64, and rows_w = 2 N: gate rows then up rows).  C [rows, N]:
+// bfloat16 with ``glu`` (the clamped gated activation), float32 or bfloat16 without.  ``rows`` bounds the grid.
+ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, const int* offsets, int E,
+                                   int rows, int N, int rows_w, int K, int glu, float limit, float alpha, int* err,
+                                   cudaStream_t stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  ME_REQUIRE(map_a && map_w && err && offsets, "me_gemm_tcgen05_grouped: missing operand");
+  ME_REQUIRE(K % 8 == 0 && K > 0 && E > 0 && rows_w == (glu ? 2 * N : N), "me_gemm_tcgen05_grouped: K %d, %d experts, %d rows of W for N %d",
+             K, E, rows_w, N);
+  ME_REQUIRE(!glu || c_dtype == ME_BF16, "me_gemm_tcgen05_grouped: the gated activation is written in bfloat16");
+  int rc;
+  if (glu) rc = launch_grouped<128, 2, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, limit, alpha, err, stream);
+  else if (c_dtype == ME_F32) rc = launch_grouped<128, 0, float>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, limit, alpha, err, stream);
+  else rc = launch_grouped<128, 0, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, limit, alpha, err, stream);
+  if (rc) return rc;
+  ME_LAUNCH_CHECK("me_gemm_tcgen05_grouped");
   return 0;
 }

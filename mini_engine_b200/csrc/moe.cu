@@ -190,6 +190,32 @@ moe_combine_kernel(const float* __restrict__ rows, int64_t rows_stride, const in
   }
 }
 
+// rows[r] = a[sorted[r] / top]: the tokens' rows in expert order, for products that read their rows by tensor-map loads.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ a, int64_t a_stride, const int* __restrict__ sorted, int top, T* __restrict__ rows, int K) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const T* src = a + (int64_t)(sorted[r] / top) * a_stride;
+  T* dst = rows + (int64_t)r * K;
+  if ((K * sizeof(T)) % 16 == 0 && (a_stride * sizeof(T)) % 16 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)rows & 15) == 0) {
+    const int n = K * (int)sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < K; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+ME_API int me_moe_gather(const void* a, int dtype, int64_t a_stride, const int* sorted, int top, void* rows, int num_rows, int K,
+                         cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  ME_DISPATCH_DTYPE(dtype, T, me_launch(moe_gather_kernel<T>, dim3(num_rows), dim3(K >= 2048 ? 256 : 128), 0, stream, (const T*)a,
+                                        a_stride, sorted, top, (T*)rows, K));
+  ME_LAUNCH_CHECK("me_moe_gather");
+  return 0;
+}
+
 ME_API int me_moe_route(const float* z, const float* bias, int T, int E, int top, int* idx, float* wgt, cudaStream_t stream) {
   if (T == 0) return 0;
   ME_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 2048, "me_moe_route: %d experts, %d chosen", E, top);

@@ -59,6 +59,8 @@ _PROTOS = {
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
+    "me_moe_gather": [_P, _I, _L, _P, _I, _P, _I, _I, _P],
+    "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
     "me_moe_combine": [_P, _L, _P, _P, _I, _P, _I, _L, _P, _I, _L, _I, _I, _P],
     "me_token_side_gate": [_P, _I, _L, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _P],
 }
@@ -1304,19 +1306,37 @@ def moe_sort(idx: torch.Tensor, num_experts: int, counts: torch.Tensor, offsets:
 
 
 use_moe_mma = True        # bfloat16 expert products on the tensor cores where the sizes allow; a switch for comparisons
+MOE_TCGEN05_MIN_ROWS = 512   # (token, choice) pairs from which the experts' products run the tcgen05 kernel (tiles of 128 rows)
 
 
 def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, offsets: torch.Tensor,
-             out: torch.Tensor, glu: Optional[tuple[float, float]] = None) -> None:
+             out: torch.Tensor, glu: Optional[tuple[float, float]] = None, workspace=None, err: Optional[torch.Tensor] = None) -> None:
     """One product per expert: ``weight`` [E, N or 2N, K]; the rows of ``a`` are gathered through ``order`` (pair id // top) or,
     without it, lie in expert order already; ``out`` [pairs, N] in expert order.  ``glu`` = (limit, alpha): the weight holds gate
-    rows then up rows and the result is the clamped gated activation."""
+    rows then up rows and the result is the clamped gated activation.
+
+    bfloat16 operands with K a multiple of 8 run on the tensor cores: from ``MOE_TCGEN05_MIN_ROWS`` pairs on (and with
+    ``workspace`` and ``err`` given) the tcgen05 kernel of csrc/gemm_tcgen05.cu over rows brought into expert order first,
+    below that the mma.sync kernel of csrc/moe_mma.cu, which gathers its rows itself; everything else the CUDA cores."""
     E, NN, K = weight.shape
     N = NN // 2 if glu else NN
     rows = out.shape[0]
     _need(weight.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and out.stride(1) == 1 and out.shape[1] == N, "moe_gemm: shapes")
     _need(order is not None or a.shape[0] == rows, "moe_gemm: rows in expert order")
     limit, alpha = glu if glu else (0.0, 0.0)
+    if (use_moe_mma and use_tcgen05_gemm and workspace is not None and err is not None and rows >= MOE_TCGEN05_MIN_ROWS
+            and a.dtype == weight.dtype == torch.bfloat16 and K % 8 == 0 and weight.data_ptr() % 16 == 0
+            and (out.dtype == torch.bfloat16 or (not glu and out.dtype == torch.float32))):
+        if order is not None:
+            gathered = workspace("moe_gathered", (rows, K), torch.bfloat16)
+            _call("me_moe_gather", a.data_ptr(), _dt(a), a.stride(0), order.data_ptr(), top, gathered.data_ptr(), rows, K, _stream())
+            a = gathered
+        if a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0:
+            _call("me_gemm_tcgen05_grouped", matrix_tensor_map(a, 128).ptr, matrix_tensor_map(weight.view(E * NN, K), 64 if glu else 128).ptr,
+                  out.data_ptr(), _dt(out), out.stride(0), offsets.data_ptr(), E, rows, N, NN, K, 1 if glu else 0, float(limit),
+                  float(alpha), err.data_ptr(), _stream())
+            return
+        order = None
     _call("me_moe_gemm", a.data_ptr(), _dt(a), a.stride(0), _ptr(order), top, weight.data_ptr(), _dt(weight), weight.stride(0),
           offsets.data_ptr(), E, out.data_ptr(), _dt(out), out.stride(0), rows, N, K, 1 if glu else 0, float(limit), float(alpha),
           1 if use_moe_mma else 0, _stream())

@@ -96,9 +96,9 @@ class RoutedExperts(FeedForward):
         place = ctx.buffer("moe_place", (T * top,), torch.int32)
         ops.moe_sort(idx, E, counts, offsets, order, place)
         act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)
-        ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha))
+        ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha), workspace=ctx.buffer, err=ctx.error_flag)
         rows = ctx.buffer("moe_rows", (T * top, W), torch.float32)
-        ops.moe_gemm(act, None, top, self._down, offsets, rows)
+        ops.moe_gemm(act, None, top, self._down, offsets, rows, workspace=ctx.buffer, err=ctx.error_flag)
         shared = self.shared.forward(x, ctx, out_name="moe_shared") if self.shared is not None else None
         out = ctx.buffer("ffn_out", (T, W), ctx.act_dtype)
         ops.moe_combine(rows, place, wgt, shared, out)

@@ -273,7 +273,7 @@ def test_clamped_gated_activation(dtype, limit):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T, E, top, W, F", [(37, 6, 2, 64, 40), (5, 5, 3, 52, 22), (130, 16, 2, 128, 64), (64, 3, 3, 40, 24),
-                                             (1, 4, 1, 64, 32), (300, 12, 1, 96, 160)])
+                                             (1, 4, 1, 64, 32), (300, 12, 1, 96, 160), (700, 8, 2, 192, 320), (1100, 5, 1, 72, 200)])
 def test_routed_experts_against_the_plain_loop(dtype, T, E, top, W, F):
     """Routing, grouping by expert, both products and the weighted sum, with and without a shared expert's output."""
     ops = _ops()
@@ -306,8 +306,11 @@ def test_routed_experts_against_the_plain_loop(dtype, T, E, top, W, F):
     gate_up = torch.stack([torch.cat((w[f"e{e}.gate"], w[f"e{e}.up"])) for e in range(E)]).to(dt).to(DEV).contiguous()
     down = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(dt).to(DEV).contiguous()
     act, rows = torch.empty(T * top, F, dtype=dt, device=DEV), torch.empty(T * top, W, device=DEV)
-    ops.moe_gemm(hd, order, top, gate_up, offsets, act, glu=(1.1, 1.702))
-    ops.moe_gemm(act, None, top, down, offsets, rows)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    work = lambda name, shape, dtype: torch.empty(shape, dtype=dtype, device=DEV)
+    ops.moe_gemm(hd, order, top, gate_up, offsets, act, glu=(1.1, 1.702), workspace=work, err=err)      # 512 pairs and more: tcgen05
+    ops.moe_gemm(act, None, top, down, offsets, rows, workspace=work, err=err)
+    assert not err.any()
     out = torch.empty(T, W, dtype=dt, device=DEV)
     ops.moe_combine(rows, place, wgt, shared.to(DEV), out)
     assert torch.allclose(out.float().cpu().double(), ref, atol=ATOL[dtype] * 3, rtol=2e-2 if dtype == "bfloat16" else 1e-5)
