@@ -59,7 +59,7 @@ conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __res
                     const int* __restrict__ positions, const int* __restrict__ token_req, const int* __restrict__ cu_seqlens,
                     const int* __restrict__ context_lens, const int* __restrict__ state_slots,
                     const int* __restrict__ slot_mapping, TO* __restrict__ q_out, TO* __restrict__ pool, int nh, int nkv, int D,
-                    int Dv, int HD, int page_size) {
+                    int Dv, int HD, int page_size, float* __restrict__ state_out, int vec2) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -72,8 +72,37 @@ conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __res
   const int i = t - tok0;
   const int slot = state_slots[b];
   const int Cq = nh * D, Ck = nkv * D;
-  float y0 = conv_output(s, wt, tok0, i, start, slot, c);
-  float y1 = two ? conv_output(s, wt, tok0, i, start, slot, c + 1) : 0.f;
+  float y0, y1 = 0.f;
+  if (two && i >= s.taps - 1) {
+    // The usual case, all taps inside this step's rows: no state, no start of the sequence, one address a tap.
+    const float* row = s.proj + (int64_t)t * s.stride + c;
+    const float b0 = s.bias ? s.bias[c] : 0.f, b1 = s.bias ? s.bias[c + 1] : 0.f;
+    if (!wt) {
+      y0 = row[0] + b0;
+      y1 = row[1] + b1;
+    } else {
+      const float* w0 = wt + (int64_t)c * s.taps;
+      const float* w1 = w0 + s.taps;
+      y0 = 0.f;
+      for (int j = 0; j < s.taps; ++j) {
+        const float* u = row - (int64_t)(s.taps - 1 - j) * s.stride;
+        float u0, u1;
+        if (vec2) {
+          const float2 v = *reinterpret_cast<const float2*>(u);
+          u0 = v.x;
+          u1 = v.y;
+        } else {
+          u0 = u[0];
+          u1 = u[1];
+        }
+        y0 = fmaf(w0[j], u0 + b0, y0);
+        y1 = fmaf(w1[j], u1 + b1, y1);
+      }
+    }
+  } else {
+    y0 = conv_output(s, wt, tok0, i, start, slot, c);
+    if (two) y1 = conv_output(s, wt, tok0, i, start, slot, c + 1);
+  }
   if (rot > 0 && c < Cq + Ck) {
     const int d = (c < Cq ? c : c - Cq) % D;        // even, since D is even when anything is rotated
     if (d < rot) {
@@ -90,6 +119,14 @@ conv_rope_kv_kernel(ConvSrc s, const float* __restrict__ wt, const double* __res
   const int where = slot_mapping ? slot_mapping[t] : -1;
   conv_store<TO>(y0, c, t, where, q_out, pool, Cq, Ck, nkv, D, Dv, HD, page_size);
   if (two) conv_store<TO>(y1, c + 1, t, where, q_out, pool, Cq, Ck, nkv, D, Dv, HD, page_size);
+  // A step in which every request brings one token: no other thread reads these channels of this slot, so the state moves
+  // on here (rows up by one, the newest u last) and the second kernel is not launched.
+  if (state_out && slot >= 0 && q_len == 1) {
+    for (int cc = c; cc < c + (two ? 2 : 1); ++cc) {
+      float* st = state_out + (int64_t)slot * (s.taps - 1) * s.C + cc;
+      for (int k = 0; k < s.taps - 1; ++k) st[(int64_t)k * s.C] = conv_input(s, tok0, k - (s.taps - 2), start, slot, cc);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -113,12 +150,13 @@ conv_state_kernel(ConvSrc s, float* __restrict__ state, const int* __restrict__ 
 
 // proj: [T, >= C] float32 with C = nh*D + (own_kv ? nkv*(D+Dv) : 0) leading channels q|k|v.  bias: [C] or null.  wt: [C, taps]
 // or null (no convolution; taps is then 1).  state: [slots, taps-1, C] float32 (unused for taps == 1).  inv_freq: [rot/2]
-// float64.  q_out: [T, nh*D]; pool: [pages][2][nkv][page_size][HD] of out_dtype (unused without own_kv).
+// float64.  single_tokens != 0: every request of the step brings one token (T == B); the state then moves on in the first
+// kernel.  q_out: [T, nh*D]; pool: [pages][2][nkv][page_size][HD] of out_dtype (unused without own_kv).
 ME_API int me_conv_rope_kv(const float* proj, int64_t proj_stride, const float* bias, const float* wt, float* state, int taps,
                            const double* inv_freq, int rot, const int* positions, const int* token_req, const int* cu_seqlens,
                            const int* context_lens, const int* state_slots, const int* slot_mapping, void* q_out, void* pool,
                            int out_dtype, int T, int B, int nh, int nkv, int D, int Dv, int HD, int own_kv, int page_size,
-                           cudaStream_t stream) {
+                           int single_tokens, cudaStream_t stream) {
   if (T == 0) return 0;
   ME_REQUIRE(T > 0 && B > 0 && nh > 0 && D > 0 && taps >= 1, "me_conv_rope_kv: bad sizes");
   ME_REQUIRE(rot % 2 == 0 && rot >= 0 && rot <= D && (rot == 0 || D % 2 == 0), "me_conv_rope_kv: %d of %d elements rotated", rot, D);
@@ -129,9 +167,11 @@ ME_API int me_conv_rope_kv(const float* proj, int64_t proj_stride, const float* 
   ME_DISPATCH_DTYPE(out_dtype, TO,
                     me_launch(conv_rope_kv_kernel<TO>, grid, dim3(threads), 0, stream, s, wt, inv_freq, rot, positions, token_req,
                               cu_seqlens, context_lens, state_slots, own_kv ? slot_mapping : (const int*)nullptr, (TO*)q_out,
-                              (TO*)pool, nh, own_kv ? nkv : 0, D, Dv, HD, page_size));
+                              (TO*)pool, nh, own_kv ? nkv : 0, D, Dv, HD, page_size,
+                              (taps > 1 && single_tokens) ? state : (float*)nullptr,
+                              (proj_stride % 2 == 0 && ((uintptr_t)proj & 7) == 0) ? 1 : 0));
   ME_LAUNCH_CHECK("me_conv_rope_kv");
-  if (taps > 1) {
+  if (taps > 1 && !single_tokens) {
     me_launch(conv_state_kernel, dim3(B, (s.C + threads - 1) / threads), dim3(threads), 0, stream, s, state, cu_seqlens,
               context_lens, state_slots);
     ME_LAUNCH_CHECK("me_conv_rope_kv (state)");

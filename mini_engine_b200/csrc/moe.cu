@@ -13,17 +13,8 @@
 // operands whose sizes allow it take the tensor-core kernel of moe_mma.cu.
 #include "common.cuh"
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ z, const float* __restrict__ bias, int E, int top, int* __restrict__ idx, float* __restrict__ wgt, int T) {
-  extern __shared__ float zs[];               // [warps][E]
-  pdl_wait();
-  pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
-  float* mine = zs + warp * E;
-  for (int e = lane; e < E; e += 32) mine[e] = z[(int64_t)t * E + e] + (bias ? bias[e] : 0.f);
-  __syncwarp();
+// One warp routes one token: ``mine`` [E] holds its logits (and is overwritten).
+__device__ __forceinline__ void route_token(float* mine, int E, int top, int lane, int* __restrict__ idx, float* __restrict__ wgt) {
   float first = 0.f, denom = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -38,19 +29,74 @@ moe_route_kernel(const float* __restrict__ z, const float* __restrict__ bias, in
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
-    if (at == 0x7fffffff) at = 0;            // every logit was NaN or -inf: keep going with a valid index
+    if (at == 0x7fffffff) at = k;            // every logit left was NaN or -inf: keep going with a valid index
     if (k == 0) first = best;
     const float p = expf(best - first);      // the first is the largest
     denom += p;
     if (lane == 0) {
-      idx[(int64_t)t * top + k] = at;
-      wgt[(int64_t)t * top + k] = p;
+      idx[k] = at;
+      wgt[k] = p;
       mine[at] = -INFINITY;
     }
     __syncwarp();
   }
-  if (lane < top) {
-    for (int k = lane; k < top; k += 32) wgt[(int64_t)t * top + k] /= denom;
+  for (int k = lane; k < top; k += 32) wgt[k] /= denom;
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, const float* __restrict__ bias, int E, int top, int* __restrict__ idx, float* __restrict__ wgt, int T) {
+  extern __shared__ float zs[];               // [warps][E]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* mine = zs + warp * E;
+  for (int e = lane; e < E; e += 32) mine[e] = z[(int64_t)t * E + e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  route_token(mine, E, top, lane, idx + (int64_t)t * top, wgt + (int64_t)t * top);
+}
+
+// Routing and grouping of a step of few tokens in ONE block (a decode step is a chain of short kernels: three launches
+// less a layer): warps route the tokens, then thread e gathers expert e's pairs in token order.
+__global__ void __launch_bounds__(256)
+moe_route_sort_small_kernel(const float* __restrict__ z, const float* __restrict__ bias, int E, int top, int T, int* __restrict__ idx,
+                            float* __restrict__ wgt, int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ place) {
+  extern __shared__ float zs[];               // [8][E] logits, then [T * top] chosen experts, then [E + 1] offsets
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, A = T * top;
+  int* chosen = reinterpret_cast<int*>(zs + 8 * E);
+  int* off = chosen + A;
+  float* mine = zs + warp * E;
+  for (int t = warp; t < T; t += 8) {
+    for (int e = lane; e < E; e += 32) mine[e] = z[(int64_t)t * E + e] + (bias ? bias[e] : 0.f);
+    __syncwarp();
+    route_token(mine, E, top, lane, idx + (int64_t)t * top, wgt + (int64_t)t * top);
+    __syncwarp();
+    for (int k = lane; k < top; k += 32) chosen[t * top + k] = idx[(int64_t)t * top + k];
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int n = 0;
+    for (int i = 0; i < A; ++i) n += chosen[i] == e;
+    off[e + 1] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    off[0] = 0;
+    for (int e = 0; e < E; ++e) off[e + 1] += off[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int at = off[e];
+    for (int i = 0; i < A; ++i)
+      if (chosen[i] == e) {
+        sorted[at] = i;
+        place[i] = at++;
+      }
   }
 }
 
@@ -232,6 +278,21 @@ ME_API int me_moe_sort(const int* idx, int T, int top, int E, int* counts, int* 
   me_launch(moe_scatter_kernel, dim3(E), dim3(256), 0, stream, idx, T * top, E, (const int*)counts, offsets, sorted, place);
   ME_LAUNCH_CHECK("me_moe_sort (scatter)");
   return 0;
+}
+
+// Routing and grouping together: one kernel for a step of few tokens, else the three kernels above.
+ME_API int me_moe_route_sort(const float* z, const float* bias, int T, int E, int top, int* idx, float* wgt, int* counts, int* offsets,
+                             int* sorted, int* place, cudaStream_t stream) {
+  if (T == 0) return 0;
+  ME_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 2048, "me_moe_route_sort: %d experts, %d chosen", E, top);
+  const size_t small = sizeof(float) * 8 * E + sizeof(int) * ((size_t)T * top + E + 1);
+  if ((int64_t)T * top <= 1024 && E <= 256 && small <= 40 * 1024) {
+    me_launch(moe_route_sort_small_kernel, dim3(1), dim3(256), small, stream, z, bias, E, top, T, idx, wgt, offsets, sorted, place);
+    ME_LAUNCH_CHECK("me_moe_route_sort");
+    return 0;
+  }
+  int rc = me_moe_route(z, bias, T, E, top, idx, wgt, stream);
+  return rc ? rc : me_moe_sort(idx, T, top, E, counts, offsets, sorted, place, stream);
 }
 
 int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top, const void* w, int64_t w_expert_stride,

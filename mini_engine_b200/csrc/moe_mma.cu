@@ -4,8 +4,9 @@
 // One block = 64 rows of one expert x 64 output columns (with ``glu``: 64 gate and the same 64 up columns, two
 // accumulators, and the clamped gated activation in the epilogue).  A block finds its expert and its rows by walking
 // the offsets (the grid has a tile to spare per expert, since the counts are known on the device only).  Four warps,
-// each a strip of 16 rows over all 64 columns.  Tiles of 32 of K arrive by cp.async in two buffers; the rows of A are
-// gathered through ``sorted``; shared-memory rows are 80 bytes apart, which keeps ldmatrix free of bank conflicts.
+// each a strip of 16 rows over all 64 columns.  Tiles of 64 of K arrive by cp.async in a ring of four buffers (a step of
+// a few tokens is bound by the experts' weights: 27 KB a stage keep about 160 KB an SM on their way); the rows of A are
+// gathered through ``sorted``; shared-memory rows are 144 bytes apart, which keeps ldmatrix free of bank conflicts.
 #include "common.cuh"
 #include "mma_prims.cuh"
 
@@ -13,15 +14,20 @@ namespace {
 
 using namespace mma_prims;
 
-constexpr int MM_BM = 64, MM_BN = 64, MM_BK = 32, MM_LD = 40, MM_THREADS = 128;
+constexpr int MM_BM = 64, MM_BN = 64, MM_BK = 64, MM_LD = 72, MM_THREADS = 128, MM_STAGES = 4;
+constexpr int MM_PIECES = MM_BK / 8;
 
 template <typename TO, bool GLU>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __restrict__ sorted, int top,
                     const bf16* __restrict__ w, int64_t w_expert_stride, const int* __restrict__ offsets, int E,
                     TO* __restrict__ out, int64_t out_stride, int N, int K, float limit, float alpha) {
-  __shared__ __align__(16) bf16 As[2][MM_BM][MM_LD];
-  __shared__ __align__(16) bf16 Ws[2][GLU ? 2 : 1][MM_BN][MM_LD];
+  extern __shared__ __align__(16) unsigned char mm_smem[];
+  constexpr int HALVES = GLU ? 2 : 1;
+  typedef bf16 (*ATile)[MM_BM][MM_LD];
+  typedef bf16 (*WTile)[HALVES][MM_BN][MM_LD];
+  ATile As = reinterpret_cast<ATile>(mm_smem);                                                    // [MM_STAGES][MM_BM][MM_LD]
+  WTile Ws = reinterpret_cast<WTile>(mm_smem + sizeof(bf16) * MM_STAGES * MM_BM * MM_LD);         // [MM_STAGES][HALVES][MM_BN][MM_LD]
   __shared__ int src_row[MM_BM];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // offsets are written by a kernel of this step
@@ -43,10 +49,10 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __r
   const bf16* wg = w + (int64_t)e * w_expert_stride;
 
   auto load = [&](int stage, int k0) {
-    // A: 64 rows x 4 pieces of 8; W: 64 (x2) rows x 4 pieces
+    // A: 64 rows x pieces of 8; W: 64 (x2) rows x pieces of 8
 #pragma unroll
-    for (int c = tid; c < MM_BM * 4; c += MM_THREADS) {
-      const int r = c >> 2, piece = c & 3;
+    for (int c = tid; c < MM_BM * MM_PIECES; c += MM_THREADS) {
+      const int r = c / MM_PIECES, piece = c % MM_PIECES;
       const int src = src_row[r];
       const bool ok = src >= 0 && k0 + piece * 8 < K;
       cp_async16(&As[stage][r][piece * 8], ok ? a + (int64_t)src * a_stride + k0 + piece * 8 : a, ok);
@@ -54,8 +60,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __r
 #pragma unroll
     for (int h = 0; h < (GLU ? 2 : 1); ++h) {
 #pragma unroll
-      for (int c = tid; c < MM_BN * 4; c += MM_THREADS) {
-        const int r = c >> 2, piece = c & 3;
+      for (int c = tid; c < MM_BN * MM_PIECES; c += MM_THREADS) {
+        const int r = c / MM_PIECES, piece = c % MM_PIECES;
         const bool ok = n0 + r < N && k0 + piece * 8 < K;
         cp_async16(&Ws[stage][h][r][piece * 8], ok ? wg + ((int64_t)h * N + n0 + r) * K + k0 + piece * 8 : wg, ok);
       }
@@ -69,19 +75,18 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __r
     if (GLU) cu[i][0] = cu[i][1] = cu[i][2] = cu[i][3] = 0.f;
   }
   const int steps = (K + MM_BK - 1) / MM_BK;
-  load(0, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int p = 0; p < MM_STAGES - 1; ++p) {        // (a group is committed every time, empty or not, so the count below holds)
+    if (p < steps) load(p, p * MM_BK);
+    cp_async_commit();
+  }
   const int mi = lane >> 3;
   for (int it = 0; it < steps; ++it) {
-    const int st = it & 1;
-    if (it + 1 < steps) {
-      load(st ^ 1, (it + 1) * MM_BK);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    const int st = it % MM_STAGES;
+    cp_async_wait<MM_STAGES - 2>();                // the group of step ``it`` has landed
+    __syncthreads();                               // ... for every thread, and the buffer of step it - 1 is free
+    if (it + MM_STAGES - 1 < steps) load((it + MM_STAGES - 1) % MM_STAGES, (it + MM_STAGES - 1) * MM_BK);
+    cp_async_commit();
 #pragma unroll
     for (int kk = 0; kk < MM_BK / 16; ++kk) {
       uint32_t af[4];
@@ -99,7 +104,6 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __r
         }
       }
     }
-    __syncthreads();                       // the buffer is free for the load after next
   }
   const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
@@ -134,12 +138,20 @@ int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top,
   ME_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && w_expert_stride % 8 == 0,
              "me_moe_gemm: operands of the tensor-core kernel must be 16-byte aligned");
   dim3 grid((rows + MM_BM - 1) / MM_BM + E, (N + MM_BN - 1) / MM_BN);
+  const size_t smem = sizeof(bf16) * MM_STAGES * (MM_BM + (glu ? 2 : 1) * MM_BN) * MM_LD;
   ME_DISPATCH_DTYPE(out_dtype, TO, {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e1 = cudaFuncSetAttribute(moe_gemm_mma_kernel<TO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+      cudaError_t e2 = cudaFuncSetAttribute(moe_gemm_mma_kernel<TO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+      ME_REQUIRE(e1 == cudaSuccess && e2 == cudaSuccess, "me_moe_gemm: cannot raise shared memory");
+      attr_set = true;
+    }
     if (glu)
-      me_launch(moe_gemm_mma_kernel<TO, true>, grid, dim3(MM_THREADS), 0, stream, (const bf16*)a, a_stride, sorted, top,
+      me_launch(moe_gemm_mma_kernel<TO, true>, grid, dim3(MM_THREADS), smem, stream, (const bf16*)a, a_stride, sorted, top,
                 (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha);
     else
-      me_launch(moe_gemm_mma_kernel<TO, false>, grid, dim3(MM_THREADS), 0, stream, (const bf16*)a, a_stride, sorted, top,
+      me_launch(moe_gemm_mma_kernel<TO, false>, grid, dim3(MM_THREADS), smem, stream, (const bf16*)a, a_stride, sorted, top,
                 (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha);
   });
   ME_LAUNCH_CHECK("me_moe_gemm (tensor cores)");

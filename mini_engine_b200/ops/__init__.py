@@ -54,10 +54,11 @@ _PROTOS = {
     "me_test_wait_expires": [_P, _I, _P, _P],
     "me_sandwich_norm": [_P, _P, _I, _P, _F, _P, _F, _P, _I, _P, _I, _I, _I, _P],
     "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P],
-    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
     "me_moe_gather": [_P, _I, _L, _P, _I, _P, _I, _I, _P],
     "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
@@ -1238,7 +1239,7 @@ def conv_rope_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_weight: 
           inv_freq.data_ptr(), rot_dims, ctx.positions.data_ptr(), ctx.token_req.data_ptr(), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), ctx.state_slots.data_ptr(), _ptr(slot_mapping) if own_kv else 0, q_out.data_ptr(),
           _ptr(pool) if own_kv else 0, _dt(q_out), T, meta.num_reqs, num_heads, num_kv_heads, dim, vdim,
-          pool.shape[-1] if own_kv else 0, 1 if own_kv else 0, page_size, _stream())
+          pool.shape[-1] if own_kv else 0, 1 if own_kv else 0, page_size, 1 if meta.num_decodes == meta.num_reqs else 0, _stream())
 
 
 use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor cores where the sizes allow; a switch for comparisons
@@ -1303,6 +1304,20 @@ def moe_sort(idx: torch.Tensor, num_experts: int, counts: torch.Tensor, offsets:
           "moe_sort: output sizes")
     _call("me_moe_sort", idx.data_ptr(), T, top, num_experts, counts.data_ptr(), offsets.data_ptr(), order.data_ptr(),
           place.data_ptr(), _stream())
+
+
+def moe_route_sort(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, weights: torch.Tensor,
+                   counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """``moe_route`` and ``moe_sort`` together; a step of few tokens does both in one kernel."""
+    T, E = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and (bias is None or (bias.dtype == torch.float32 and bias.numel() == E)),
+          "moe_route_sort: logits and bias must be float32")
+    _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
+          and idx.is_contiguous() and weights.is_contiguous(), "moe_route_sort: outputs are [T, top]")
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (counts, offsets, order, place)) and counts.numel() >= E
+          and offsets.numel() >= E + 1 and order.numel() >= T * top and place.numel() >= T * top, "moe_route_sort: output sizes")
+    _call("me_moe_route_sort", logits.data_ptr(), _ptr(bias), T, E, top, idx.data_ptr(), weights.data_ptr(), counts.data_ptr(),
+          offsets.data_ptr(), order.data_ptr(), place.data_ptr(), _stream())
 
 
 use_moe_mma = True        # bfloat16 expert products on the tensor cores where the sizes allow; a switch for comparisons

@@ -89,12 +89,11 @@ class RoutedExperts(FeedForward):
         z = self.router.forward(x, ctx, "moe_logits", out_dtype=torch.float32)
         idx = ctx.buffer("moe_idx", (T, top), torch.int32)
         wgt = ctx.buffer("moe_weights", (T, top), torch.float32)
-        ops.moe_route(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt)
         counts = ctx.buffer("moe_counts", (E,), torch.int32)
         offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32)
         order = ctx.buffer("moe_order", (T * top,), torch.int32)
         place = ctx.buffer("moe_place", (T * top,), torch.int32)
-        ops.moe_sort(idx, E, counts, offsets, order, place)
+        ops.moe_route_sort(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt, counts, offsets, order, place)
         act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)
         ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha), workspace=ctx.buffer, err=ctx.error_flag)
         rows = ctx.buffer("moe_rows", (T * top, W), torch.float32)

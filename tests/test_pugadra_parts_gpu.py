@@ -303,6 +303,10 @@ def test_routed_experts_against_the_plain_loop(dtype, T, E, top, W, F):
     assert sorted(order.cpu().tolist()) == list(range(T * top)) and torch.equal(order[place.long()].cpu(), torch.arange(T * top, dtype=torch.int32))
     by_expert = flat[order.cpu().long()]
     assert torch.equal(by_expert, by_expert.sort().values)
+    # routing and grouping in one call (one kernel for few tokens) gives the same
+    both = [torch.empty_like(t) for t in (idx, wgt, counts, offsets, order, place)]
+    ops.moe_route_sort(z, w["router.b"].float().to(DEV), top, *both)
+    assert all(torch.equal(a, b) for a, b in zip((idx, wgt, offsets, order, place), (both[0], both[1], both[3], both[4], both[5])))
     gate_up = torch.stack([torch.cat((w[f"e{e}.gate"], w[f"e{e}.up"])) for e in range(E)]).to(dt).to(DEV).contiguous()
     down = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(dt).to(DEV).contiguous()
     act, rows = torch.empty(T * top, F, dtype=dt, device=DEV), torch.empty(T * top, W, device=DEV)
