@@ -728,7 +728,7 @@ def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
     that their summed time makes: bytes for the element-wise kernels, multiply-adds for attention and the experts."""
     W = cfg["width"]
     side = cfg.get("token_side", {}).get("dim", 0)
-    need = {k: 0.0 for k in ("me_sandwich_norm", "me_conv_rope_kv", "me_sink_attn", "me_attn_prefill_tcgen05", "me_clamped_glu", "me_moe_gemm",
+    need = {k: 0.0 for k in ("me_sandwich_norm", "me_conv_rope_kv", "me_sink_attn", "me_attn_prefill_tcgen05", "me_clamped_glu", "me_moe_gemm", "me_gemm_tcgen05_grouped",
                              "me_moe_combine", "me_token_side_gate")}
     for layer in cfg["layers"]:
         m, mlp = layer["mixer"], layer["mlp"]
@@ -745,12 +745,13 @@ def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
             need["me_clamped_glu"] += T * mlp["ff"] * 3 * item
         elif mlp is not None:
             need["me_moe_gemm"] += 6.0 * T * mlp["router"]["top"] * mlp["expert"]["ff"] * W
+            need["me_gemm_tcgen05_grouped"] += 6.0 * T * mlp["router"]["top"] * mlp["expert"]["ff"] * W
             need["me_moe_combine"] += T * W * (4 * mlp["router"]["top"] + 2 * item)
             if mlp.get("shared"):
                 need["me_clamped_glu"] += T * mlp["shared"]["ff"] * 3 * item
         if side:
             need["me_token_side_gate"] += T * side * (4 + 2 * item)
-    return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_moe_gemm"), times, pk)
+    return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_moe_gemm", "me_gemm_tcgen05_grouped"), times, pk)
 
 
 def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
@@ -761,7 +762,14 @@ def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict
     att = 4.0 * H * D * _window_pairs(T, window) * L
     need = {"me_add_rmsnorm": 2 * L * T * W * (8 + 2 * item), "me_qk_norm_rope_kv_write": L * T * (H + 2 * G) * D * 2 * item,
             "me_attn_prefill_tcgen05": att, "me_attn_prefill": att}
-    return _fractions(need, ("me_attn_prefill_tcgen05", "me_attn_prefill"), times, pk)
+    out = _fractions(need, ("me_attn_prefill_tcgen05", "me_attn_prefill"), times, pk)
+    # all products of the layers together (the tcgen05 kernels in their three forms)
+    flops = 2.0 * L * T * (W * (H + 2 * G) * D + H * D * W + 3 * W * cfg["intermediate_size"])
+    us = sum(times.get(k, {}).get("us", 0.0) for k in ("me_gemm_tcgen05", "me_gemm_tcgen05_persistent", "me_gemm_tcgen05_shared"))
+    if us:
+        out["layer products (tcgen05)"] = {"us": round(us, 1), "flops": flops, "frac": round(flops / (us * 1e-6) / (pk["bf16_tflops"] * 1e12), 4),
+                                           "of": "bf16_tflops"}
+    return out
 
 
 def run_design_mode(args, design: str) -> int:
