@@ -54,15 +54,18 @@ _PROTOS = {
     "me_test_wait_expires": [_P, _I, _P, _P],
     "me_sandwich_norm": [_P, _P, _I, _P, _F, _P, _F, _P, _I, _P, _I, _I, _I, _P],
     "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P],
-    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "me_rope_table": [_P, _P, _I, _I, _P, _P],
     "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "me_moe_route_sort_fused": [_P, _I, _L, _P, _I, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P],
     "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
     "me_moe_gather": [_P, _I, _L, _P, _I, _P, _I, _I, _P],
     "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
     "me_moe_combine": [_P, _L, _P, _P, _I, _P, _I, _L, _P, _I, _L, _I, _I, _P],
+    "me_token_side_fused": [_P, _P, _I, _P, _F, _F, _P, _P, _I, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _I, _P],
     "me_token_side_gate": [_P, _I, _L, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _P],
 }
 _DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -103,6 +106,7 @@ def require_extension() -> ctypes.CDLL:
     lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     lib.me_latent_attention_mma_takes.argtypes = [_I, _I]
+    lib.me_moe_route_sort_is_small.argtypes = [_I, _I, _I]
     lib.me_latent_attention_mma_heads_per_block.argtypes = [_I]
     _lib = lib
     return lib
@@ -1215,7 +1219,7 @@ def clamped_glu(x: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) 
 def conv_rope_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_weight: Optional[torch.Tensor],
                  state: Optional[torch.Tensor], inv_freq: torch.Tensor, rot_dims: int, ctx, slot_mapping: Optional[torch.Tensor],
                  q_out: torch.Tensor, pool: Optional[torch.Tensor], page_size: int, num_heads: int, num_kv_heads: int, dim: int,
-                 vdim: int, own_kv: bool) -> None:
+                 vdim: int, own_kv: bool, angles: Optional[torch.Tensor] = None) -> None:
     """From the packed float32 projections q|k|v (the leading columns of ``proj``): bias, the short causal convolution with
     its state, the rotation of neighbouring pairs, queries to ``q_out`` and keys and values into the cache rows that
     ``slot_mapping`` names (see csrc/conv_rope_kv.cu).  Without ``own_kv`` only the queries exist."""
@@ -1239,7 +1243,20 @@ def conv_rope_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_weight: 
           inv_freq.data_ptr(), rot_dims, ctx.positions.data_ptr(), ctx.token_req.data_ptr(), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), ctx.state_slots.data_ptr(), _ptr(slot_mapping) if own_kv else 0, q_out.data_ptr(),
           _ptr(pool) if own_kv else 0, _dt(q_out), T, meta.num_reqs, num_heads, num_kv_heads, dim, vdim,
-          pool.shape[-1] if own_kv else 0, 1 if own_kv else 0, page_size, 1 if meta.num_decodes == meta.num_reqs else 0, _stream())
+          pool.shape[-1] if own_kv else 0, 1 if own_kv else 0, page_size, 1 if meta.num_decodes == meta.num_reqs else 0,
+          _ptr(angles), _stream())
+
+
+ROPE_TABLE_MIN_TOKENS = 64     # steps from this many tokens on form the rotation's cosines and sines once for all layers
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
+    """``out`` [T, rot_dims / 2, 2] float32: (cosine, sine) of position x frequency for every token of the step, the angle
+    formed in double precision as ``conv_rope_kv`` forms it."""
+    T, half = positions.shape[0], inv_freq.numel()
+    _need(inv_freq.dtype == torch.float64 and out.dtype == torch.float32 and out.is_contiguous() and out.numel() == T * half * 2,
+          "rope_table: inv_freq float64 [half], out float32 [T, half, 2]")
+    _call("me_rope_table", positions.data_ptr(), inv_freq.data_ptr(), half, T, out.data_ptr(), _stream())
 
 
 use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor cores where the sizes allow; a switch for comparisons
@@ -1320,6 +1337,26 @@ def moe_route_sort(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int,
           offsets.data_ptr(), order.data_ptr(), place.data_ptr(), _stream())
 
 
+def moe_route_sort_is_small(T: int, E: int, top: int) -> bool:
+    """Whether a step of T tokens is routed and grouped by one block, which can form the router's product as well."""
+    return bool((_lib or require_extension()).me_moe_route_sort_is_small(T, E, top))
+
+
+def moe_route_sort_fused(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
+                         weights: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """``moe_route_sort`` for a short step with the router's product ``x @ router.T`` (float32 sums) formed in the same kernel."""
+    T, W = x.shape
+    E = router.shape[0]
+    _need(x.stride(1) == 1 and router.is_contiguous() and router.shape[1] == W, "moe_route_sort_fused: x [T, W], router [E, W]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route_sort_fused: bias must be float32 [E]")
+    _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
+          and idx.is_contiguous() and weights.is_contiguous(), "moe_route_sort_fused: outputs are [T, top]")
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (offsets, order, place)) and offsets.numel() >= E + 1
+          and order.numel() >= T * top and place.numel() >= T * top, "moe_route_sort_fused: output sizes")
+    _call("me_moe_route_sort_fused", x.data_ptr(), _dt(x), x.stride(0), router.data_ptr(), _dt(router), W, _ptr(bias), T, E, top,
+          idx.data_ptr(), weights.data_ptr(), offsets.data_ptr(), order.data_ptr(), place.data_ptr(), _stream())
+
+
 use_moe_mma = True        # bfloat16 expert products on the tensor cores where the sizes allow; a switch for comparisons
 MOE_TCGEN05_MIN_ROWS = 512   # (token, choice) pairs from which the experts' products run the tcgen05 kernel (tiles of 128 rows)
 
@@ -1376,3 +1413,25 @@ def token_side_gate(z: torch.Tensor, token_ids: torch.Tensor, feedback: Optional
     _need(token_ids.dtype == torch.int32 and token_ids.numel() == T, "token_side_gate: token ids must be int32 [T]")
     _call("me_token_side_gate", z.data_ptr(), _dt(z), z.stride(0), token_ids.data_ptr(), _ptr(feedback), table.data_ptr(), _dt(table),
           table.stride(0), table.shape[0], first, dim, out.data_ptr(), _dt(out), T, _stream())
+
+
+TOKEN_SIDE_FUSED_MAX_TOKENS = 128    # steps up to this many tokens run a layer's token input as ONE kernel
+
+
+def token_side_fused(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor], mult: float, eps: float,
+                     w_gate: torch.Tensor, w_proj: torch.Tensor, token_ids: torch.Tensor, feedback: Optional[torch.Tensor],
+                     table: torch.Tensor, first: int, out: torch.Tensor) -> None:
+    """For steps of few tokens, in one kernel: ``residual += mult * y / rms(y) * post_weight`` (skipped without ``y``), then
+    ``out = W_proj (gelu_tanh(W_gate x) * table[token, first : first + dim])`` with x the new residual in ``out``'s dtype."""
+    T, W = residual.shape
+    dim = w_gate.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, W),
+          "token_side_fused: residual float32 [T, W], out [T, W]")
+    _need(y is None or (tuple(y.shape) == (T, W) and y.is_contiguous() and post_weight is not None and post_weight.dtype == torch.float32),
+          "token_side_fused: y must be [T, W] with a float32 weight")
+    _need(w_gate.is_contiguous() and w_proj.is_contiguous() and tuple(w_gate.shape) == (dim, W) and tuple(w_proj.shape) == (W, dim)
+          and w_gate.dtype == w_proj.dtype and table.is_contiguous(), "token_side_fused: weights [dim, W] and [W, dim] of one dtype")
+    _need(token_ids.dtype == torch.int32 and token_ids.numel() == T, "token_side_fused: token ids must be int32 [T]")
+    _call("me_token_side_fused", residual.data_ptr(), _ptr(y), _dt(y) if y is not None else 0, _ptr(post_weight), float(mult), float(eps),
+          w_gate.data_ptr(), w_proj.data_ptr(), _dt(w_gate), token_ids.data_ptr(), _ptr(feedback), table.data_ptr(), _dt(table),
+          table.stride(0), table.shape[0], first, dim, out.data_ptr(), _dt(out), T, W, _stream())

@@ -97,10 +97,19 @@ class SinkAttention(Mixer):
         kv = ctx.kv_cache(call.cache_slot if self.own_kv else call.kv_slot)
         q = ctx.buffer("attn_q", (T, H * D), ctx.act_dtype)
         inv_freq = self.rope.inv_freq if self.rope is not None else self._no_freq
+        angles = None
+        if self.rope is not None and T >= ops.ROPE_TABLE_MIN_TOKENS:
+            # one table a step for all layers that share the rotation (the step's metadata object lives as long as the step)
+            tables = ctx.attn_meta.__dict__.setdefault("rope_tables", {})
+            angles = tables.get(id(self.rope))
+            if angles is None:
+                angles = tables[id(self.rope)] = ctx.buffer(f"rope_table_{self.rope.rotary_dim}_{self.rope.theta!r}",
+                                                            (T, inv_freq.numel(), 2), torch.float32)
+                ops.rope_table(ctx.positions, inv_freq, angles)
         ops.conv_rope_kv(proj, self.p("in_bias") if self.has_bias else None, self.p("in_conv") if self.taps >= 1 else None,
                          ctx.state(call.cache_slot, "conv") if self.taps > 1 else None, inv_freq, inv_freq.numel() * 2, ctx,
                          kv.slot_mapping if self.own_kv and call.writes_cache else None, q, kv.pool, kv.page_size, H, G, D, V,
-                         self.own_kv and call.writes_cache)
+                         self.own_kv and call.writes_cache, angles=angles)
         out = ctx.buffer("attn_out", (T, H * V), ctx.act_dtype)
         gate = proj[:, self.channels:] if self.has_gate else None
         ops.sink_attention(q, gate, out, kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta, H, G, D, V, self.scale,
