@@ -58,12 +58,9 @@ moe_route_kernel(const float* __restrict__ z, const float* __restrict__ bias, in
 }
 
 // Routing and grouping of a step of few tokens in ONE block (a decode step is a chain of short kernels: three launches
-// less a layer, four when the router's product is formed here too): warps route the tokens, then thread e gathers expert
-// e's pairs in token order.
-template <typename TX, typename TW>
+// less a layer): warps route the tokens, then thread e gathers expert e's pairs in token order.
 __global__ void __launch_bounds__(256)
-moe_route_sort_small_kernel(const float* __restrict__ z, const TX* __restrict__ x, int64_t x_stride, const TW* __restrict__ router,
-                            int W, const float* __restrict__ bias, int E, int top, int T, int* __restrict__ idx,
+moe_route_sort_small_kernel(const float* __restrict__ z, const float* __restrict__ bias, int E, int top, int T, int* __restrict__ idx,
                             float* __restrict__ wgt, int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ place) {
   extern __shared__ float zs[];               // [8][E] logits, then [T * top] chosen experts, then [E + 1] offsets
   pdl_wait();
@@ -73,19 +70,7 @@ moe_route_sort_small_kernel(const float* __restrict__ z, const TX* __restrict__ 
   int* off = chosen + A;
   float* mine = zs + warp * E;
   for (int t = warp; t < T; t += 8) {
-    if (z) {
-      for (int e = lane; e < E; e += 32) mine[e] = z[(int64_t)t * E + e] + (bias ? bias[e] : 0.f);
-    } else {
-      // the router's product itself (float32 sums over the token's row), an expert at a time
-      const TX* xr = x + (int64_t)t * x_stride;
-      for (int e = 0; e < E; ++e) {
-        const TW* wr = router + (int64_t)e * W;
-        float acc = 0.f;
-        for (int i = lane; i < W; i += 32) acc = fmaf(to_f<TX>(xr[i]), to_f<TW>(wr[i]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) mine[e] = acc + (bias ? bias[e] : 0.f);
-      }
-    }
+    for (int e = lane; e < E; e += 32) mine[e] = z[(int64_t)t * E + e] + (bias ? bias[e] : 0.f);
     __syncwarp();
     route_token(mine, E, top, lane, idx + (int64_t)t * top, wgt + (int64_t)t * top);
     __syncwarp();
@@ -302,33 +287,12 @@ ME_API int me_moe_route_sort(const float* z, const float* bias, int T, int E, in
   ME_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 2048, "me_moe_route_sort: %d experts, %d chosen", E, top);
   const size_t small = sizeof(float) * 8 * E + sizeof(int) * ((size_t)T * top + E + 1);
   if ((int64_t)T * top <= 1024 && E <= 256 && small <= 40 * 1024) {
-    me_launch(moe_route_sort_small_kernel<float, float>, dim3(1), dim3(256), small, stream, z, (const float*)nullptr, (int64_t)0,
-              (const float*)nullptr, 0, bias, E, top, T, idx, wgt, offsets, sorted, place);
+    me_launch(moe_route_sort_small_kernel, dim3(1), dim3(256), small, stream, z, bias, E, top, T, idx, wgt, offsets, sorted, place);
     ME_LAUNCH_CHECK("me_moe_route_sort");
     return 0;
   }
   int rc = me_moe_route(z, bias, T, E, top, idx, wgt, stream);
   return rc ? rc : me_moe_sort(idx, T, top, E, counts, offsets, sorted, place, stream);
-}
-
-// Whether a step of T tokens routes and groups in one block (and may then form the router's product there as well).
-ME_API int me_moe_route_sort_is_small(int T, int E, int top) {
-  return (int64_t)T * top <= 1024 && E <= 256 && sizeof(float) * 8 * E + sizeof(int) * ((size_t)T * top + E + 1) <= 40 * 1024;
-}
-
-// As me_moe_route_sort for a short step (me_moe_route_sort_is_small), with the router's logits formed in the same kernel:
-// x [T, W], router [E, W], float32 sums.
-ME_API int me_moe_route_sort_fused(const void* x, int x_dtype, int64_t x_stride, const void* router, int w_dtype, int W,
-                                   const float* bias, int T, int E, int top, int* idx, float* wgt, int* offsets, int* sorted,
-                                   int* place, cudaStream_t stream) {
-  if (T == 0) return 0;
-  ME_REQUIRE(me_moe_route_sort_is_small(T, E, top) && top >= 1 && top <= E, "me_moe_route_sort_fused: %d tokens, %d experts, %d chosen", T, E, top);
-  const size_t small = sizeof(float) * 8 * E + sizeof(int) * ((size_t)T * top + E + 1);
-  ME_DISPATCH_DTYPE(x_dtype, TX, ME_DISPATCH_DTYPE(w_dtype, TW,
-      me_launch(moe_route_sort_small_kernel<TX, TW>, dim3(1), dim3(256), small, stream, (const float*)nullptr, (const TX*)x, x_stride,
-                (const TW*)router, W, bias, E, top, T, idx, wgt, offsets, sorted, place)));
-  ME_LAUNCH_CHECK("me_moe_route_sort_fused");
-  return 0;
 }
 
 int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top, const void* w, int64_t w_expert_stride,

@@ -59,13 +59,11 @@ _PROTOS = {
     "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
-    "me_moe_route_sort_fused": [_P, _I, _L, _P, _I, _I, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P],
     "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
     "me_moe_gather": [_P, _I, _L, _P, _I, _P, _I, _I, _P],
     "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
     "me_moe_combine": [_P, _L, _P, _P, _I, _P, _I, _L, _P, _I, _L, _I, _I, _P],
-    "me_token_side_fused": [_P, _P, _I, _P, _F, _F, _P, _P, _I, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _I, _P],
     "me_token_side_gate": [_P, _I, _L, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _P],
 }
 _DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -106,7 +104,6 @@ def require_extension() -> ctypes.CDLL:
     lib.me_attn_decode_fused_takes.argtypes = [_I, _I]
     lib.me_gemm_skinny_splits.argtypes = [_I]
     lib.me_latent_attention_mma_takes.argtypes = [_I, _I]
-    lib.me_moe_route_sort_is_small.argtypes = [_I, _I, _I]
     lib.me_latent_attention_mma_heads_per_block.argtypes = [_I]
     _lib = lib
     return lib
@@ -1337,26 +1334,6 @@ def moe_route_sort(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int,
           offsets.data_ptr(), order.data_ptr(), place.data_ptr(), _stream())
 
 
-def moe_route_sort_is_small(T: int, E: int, top: int) -> bool:
-    """Whether a step of T tokens is routed and grouped by one block, which can form the router's product as well."""
-    return bool((_lib or require_extension()).me_moe_route_sort_is_small(T, E, top))
-
-
-def moe_route_sort_fused(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
-                         weights: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
-    """``moe_route_sort`` for a short step with the router's product ``x @ router.T`` (float32 sums) formed in the same kernel."""
-    T, W = x.shape
-    E = router.shape[0]
-    _need(x.stride(1) == 1 and router.is_contiguous() and router.shape[1] == W, "moe_route_sort_fused: x [T, W], router [E, W]")
-    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route_sort_fused: bias must be float32 [E]")
-    _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
-          and idx.is_contiguous() and weights.is_contiguous(), "moe_route_sort_fused: outputs are [T, top]")
-    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (offsets, order, place)) and offsets.numel() >= E + 1
-          and order.numel() >= T * top and place.numel() >= T * top, "moe_route_sort_fused: output sizes")
-    _call("me_moe_route_sort_fused", x.data_ptr(), _dt(x), x.stride(0), router.data_ptr(), _dt(router), W, _ptr(bias), T, E, top,
-          idx.data_ptr(), weights.data_ptr(), offsets.data_ptr(), order.data_ptr(), place.data_ptr(), _stream())
-
-
 use_moe_mma = True        # bfloat16 expert products on the tensor cores where the sizes allow; a switch for comparisons
 MOE_TCGEN05_MIN_ROWS = 512   # (token, choice) pairs from which the experts' products run the tcgen05 kernel (tiles of 128 rows)
 
@@ -1413,25 +1390,3 @@ def token_side_gate(z: torch.Tensor, token_ids: torch.Tensor, feedback: Optional
     _need(token_ids.dtype == torch.int32 and token_ids.numel() == T, "token_side_gate: token ids must be int32 [T]")
     _call("me_token_side_gate", z.data_ptr(), _dt(z), z.stride(0), token_ids.data_ptr(), _ptr(feedback), table.data_ptr(), _dt(table),
           table.stride(0), table.shape[0], first, dim, out.data_ptr(), _dt(out), T, _stream())
-
-
-TOKEN_SIDE_FUSED_MAX_TOKENS = 128    # steps up to this many tokens run a layer's token input as ONE kernel
-
-
-def token_side_fused(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor], mult: float, eps: float,
-                     w_gate: torch.Tensor, w_proj: torch.Tensor, token_ids: torch.Tensor, feedback: Optional[torch.Tensor],
-                     table: torch.Tensor, first: int, out: torch.Tensor) -> None:
-    """For steps of few tokens, in one kernel: ``residual += mult * y / rms(y) * post_weight`` (skipped without ``y``), then
-    ``out = W_proj (gelu_tanh(W_gate x) * table[token, first : first + dim])`` with x the new residual in ``out``'s dtype."""
-    T, W = residual.shape
-    dim = w_gate.shape[0]
-    _need(residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, W),
-          "token_side_fused: residual float32 [T, W], out [T, W]")
-    _need(y is None or (tuple(y.shape) == (T, W) and y.is_contiguous() and post_weight is not None and post_weight.dtype == torch.float32),
-          "token_side_fused: y must be [T, W] with a float32 weight")
-    _need(w_gate.is_contiguous() and w_proj.is_contiguous() and tuple(w_gate.shape) == (dim, W) and tuple(w_proj.shape) == (W, dim)
-          and w_gate.dtype == w_proj.dtype and table.is_contiguous(), "token_side_fused: weights [dim, W] and [W, dim] of one dtype")
-    _need(token_ids.dtype == torch.int32 and token_ids.numel() == T, "token_side_fused: token ids must be int32 [T]")
-    _call("me_token_side_fused", residual.data_ptr(), _ptr(y), _dt(y) if y is not None else 0, _ptr(post_weight), float(mult), float(eps),
-          w_gate.data_ptr(), w_proj.data_ptr(), _dt(w_gate), token_ids.data_ptr(), _ptr(feedback), table.data_ptr(), _dt(table),
-          table.stride(0), table.shape[0], first, dim, out.data_ptr(), _dt(out), T, W, _stream())

@@ -227,13 +227,9 @@ class SandwichNormBlock(Block):
             y = self.feed_forward.forward(self.feed_forward_norm.forward(residual, update, ctx), ctx)
             update = NormedUpdate(y, self.post_feed_forward_norm.weight, eps, self.mult)
         if self.side is not None:
-            if residual.shape[0] <= ops.TOKEN_SIDE_FUSED_MAX_TOKENS and (self.side.hidden_size + self.side.dim) * 4 <= 96 * 1024:
-                y = self.side.forward_pending(residual, update, ctx)          # one kernel where the step is a chain of short ones
-            else:
-                x = ctx.buffer("stream_copy", tuple(residual.shape), ctx.act_dtype)
-                ops.sandwich_norm(residual, update.y, update.weight, update.mult, None, eps, x, norm_out=False)
-                y = self.side.forward(x, ctx)
-            update = NormedUpdate(y, self.side.p(self.side.norm), eps, self.mult)
+            x = ctx.buffer("stream_copy", tuple(residual.shape), ctx.act_dtype)
+            ops.sandwich_norm(residual, update.y, update.weight, update.mult, None, eps, x, norm_out=False)
+            update = NormedUpdate(self.side.forward(x, ctx), self.side.p(self.side.norm), eps, self.mult)
         return update
 
 

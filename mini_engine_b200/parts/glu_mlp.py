@@ -86,18 +86,14 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         E, F, W, top = self.num_experts, self.expert_size, self.hidden_size, self.top
         T = x.shape[0]
+        z = self.router.forward(x, ctx, "moe_logits", out_dtype=torch.float32)
         idx = ctx.buffer("moe_idx", (T, top), torch.int32)
         wgt = ctx.buffer("moe_weights", (T, top), torch.float32)
         counts = ctx.buffer("moe_counts", (E,), torch.int32)
         offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32)
         order = ctx.buffer("moe_order", (T * top,), torch.int32)
         place = ctx.buffer("moe_place", (T * top,), torch.int32)
-        bias = self.p("router.b") if self.has_router_bias else None
-        if ops.moe_route_sort_is_small(T, E, top):       # a short step: the router's product, routing and grouping in one kernel
-            ops.moe_route_sort_fused(x, self.router.weight, bias, top, idx, wgt, offsets, order, place)
-        else:
-            z = self.router.forward(x, ctx, "moe_logits", out_dtype=torch.float32)
-            ops.moe_route_sort(z, bias, top, idx, wgt, counts, offsets, order, place)
+        ops.moe_route_sort(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt, counts, offsets, order, place)
         act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)
         ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha), workspace=ctx.buffer, err=ctx.error_flag)
         rows = ctx.buffer("moe_rows", (T * top, W), torch.float32)

@@ -33,13 +33,6 @@ class TokenSideInput(Part):
     def param_decls(self):
         return [ParamDecl(self.norm, (self.hidden_size,), init="norm", role="vector")]
 
-    def forward_pending(self, residual: torch.Tensor, update, ctx) -> torch.Tensor:
-        """For a step of few tokens: the pending ``NormedUpdate`` goes into ``residual`` and y comes out, in one kernel."""
-        out = ctx.buffer("side_y", tuple(residual.shape), ctx.act_dtype)
-        ops.token_side_fused(residual, update.y, update.weight, update.mult, update.eps, self.gate.weight, self.proj.weight,
-                             ctx.token_ids, ctx.token_feedback, self.table.p(self.table.param), self.first, out)
-        return out
-
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         """``x`` [T, hidden]: the residual stream in the working dtype -> y [T, hidden]."""
         z = self.gate.forward(x, ctx, "side_z", out_dtype=torch.float32)

@@ -313,11 +313,6 @@ def test_routed_experts_against_the_plain_loop(dtype, T, E, top, W, F):
     both = [torch.empty_like(t) for t in (idx, wgt, counts, offsets, order, place)]
     ops.moe_route_sort(z, w["router.b"].float().to(DEV), top, *both)
     assert all(torch.equal(a, b) for a, b in zip((idx, wgt, offsets, order, place), (both[0], both[1], both[3], both[4], both[5])))
-    if ops.moe_route_sort_is_small(T, E, top):              # ... and with the router's product formed in the same kernel
-        fused = [torch.empty_like(t) for t in (idx, wgt, offsets, order, place)]
-        ops.moe_route_sort_fused(hd, w["router"].to(dt).to(DEV), w["router.b"].float().to(DEV), top, *fused)
-        assert torch.equal(fused[0], idx) and torch.allclose(fused[1], wgt, atol=1e-5) and all(
-            torch.equal(a, b) for a, b in zip(fused[2:], (offsets, order, place)))
     gate_up = torch.stack([torch.cat((w[f"e{e}.gate"], w[f"e{e}.up"])) for e in range(E)]).to(dt).to(DEV).contiguous()
     down = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(dt).to(DEV).contiguous()
     act, rows = torch.empty(T * top, F, dtype=dt, device=DEV), torch.empty(T * top, W, device=DEV)
@@ -345,27 +340,3 @@ def test_gated_slice_of_the_second_embedding(dtype):
     out = torch.empty(T, dim, dtype=DT[dtype], device=DEV)
     ops.token_side_gate(z.to(DEV), ids.to(DEV), None, table.to(DEV), layer * dim, out)
     assert torch.allclose(out.float().cpu().double(), ref, atol=ATOL[dtype], rtol=1e-2 if dtype == "bfloat16" else 1e-5)
-
-
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("W, dim", [(64, 8), (52, 5), (1024, 64)])
-def test_token_input_of_a_short_step_in_one_kernel(dtype, W, dim):
-    """The pending update of the stream, the gate, the table's slice and the projection against the plain functions."""
-    ops = _ops()
-    dt = DT[dtype]
-    T, layers, vocab, layer, eps, mult = 7, 3, 40, 1, 1e-5, 0.4
-    x = torch.randn(T, W, generator=g(0)) * 2
-    y = (torch.randn(T, W, generator=g(1)) * 3).to(dt)
-    wb = torch.randn(W, generator=g(2)) * 0.3
-    w = {"side.embed": torch.randn(vocab, dim * layers, generator=g(3)).to(dt).double(),
-         "l.side.gate": (torch.randn(dim, W, generator=g(4)) / W ** 0.5).to(dt).double(),
-         "l.side.proj": (torch.randn(W, dim, generator=g(5)) / dim ** 0.5).to(dt).double(), "l.side.norm": torch.ones(W).double()}
-    ids = torch.randint(0, vocab, (T,), generator=g(6), dtype=torch.int32)
-    new = x.double() + mult * plain.norm_around_zero(y.double(), wb.double(), eps)
-    e = w["side.embed"][ids.long()][:, layer * dim:(layer + 1) * dim]
-    ref = (plain.gelu_tanh(new @ w["l.side.gate"].T) * e) @ w["l.side.proj"].T
-    xd, out = x.to(DEV), torch.empty(T, W, dtype=dt, device=DEV)
-    ops.token_side_fused(xd, y.to(DEV), (1 + wb).to(DEV), mult, eps, w["l.side.gate"].to(dt).to(DEV), w["l.side.proj"].to(dt).to(DEV),
-                         ids.to(DEV), None, w["side.embed"].to(dt).to(DEV), layer * dim, out)
-    assert torch.allclose(xd.cpu().double(), new, atol=1e-5)
-    assert torch.allclose(out.float().cpu().double(), ref, atol=ATOL[dtype] * 2, rtol=2e-2 if dtype == "bfloat16" else 1e-5)
