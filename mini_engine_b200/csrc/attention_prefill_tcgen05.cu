@@ -525,7 +525,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
   } else {
     const int lane_base = (warp & 3) * 32, g = (warp - 2) >> 2;
     const int r = lane_base + lane;
-    const int hh = r / tq, tk = r % tq;
+    const int tk = r % tq;
     const bool row_ok = tk < n_tok;
     const int pos = p_lo + tk;
     const uint32_t t_row = (uint32_t)lane_base << 16;
@@ -696,11 +696,6 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
         float o_acc[32];
         tc5::ld_32cols(tmem_o + t_row + g * OC + c0, o_acc);
         tc5::wait_ld();
-        if (gate && row_ok) {                                // the output times the sigmoid of the gate's pre-activation
-          const float* gr = gate + (int64_t)(tok0 + q0 + tk) * gate_stride + (int64_t)(head0 + hh) * HD + g * OC + c0;
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) o_acc[jj] = __fdividef(o_acc[jj], 1.f + __expf(-gr[jj]));
-        }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 pk;
@@ -719,7 +714,18 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
       for (int row = (warp - 2) * 16 + lane / PIECES; row < (warp - 1) * 16; row += ROWS_AT_ONCE) {
         const int tok = row % tq;
         if (tok < n_tok) {
-          const uint4 pk = *reinterpret_cast<const uint4*>(q_s + row * (HD * 2) + ((piece ^ (row & 7)) << 4));
+          uint4 pk = *reinterpret_cast<const uint4*>(q_s + row * (HD * 2) + ((piece ^ (row & 7)) << 4));
+          if (gate) {
+            // The output times the sigmoid of the gate's pre-activation, here where the lanes of a row read the gate's row
+            // side by side (a lane a row, at the read-out from tensor memory, took 32 lines a load).
+            const float* gr = gate + (int64_t)(tok0 + q0 + tok) * gate_stride + (int64_t)(head0 + row / tq) * HD + piece * 8;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const float2 v = __bfloat1622float2(h2[jj]);
+              h2[jj] = __floats2bfloat162_rn(__fdividef(v.x, 1.f + __expf(-gr[2 * jj])), __fdividef(v.y, 1.f + __expf(-gr[2 * jj + 1])));
+            }
+          }
           *reinterpret_cast<uint4*>(out + (int64_t)(tok0 + q0 + tok) * out_row_stride + (int64_t)(head0 + row / tq) * HD + piece * 8) = pk;
         }
       }
