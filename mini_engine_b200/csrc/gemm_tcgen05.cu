@@ -50,24 +50,25 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], in
 // tile's products at K = 1,024); the results go through ``stage`` (4 KB of shared memory of the warp's own, 128-byte
 // aligned) in groups of 128 bytes a row, swizzled by 16-byte pieces, and leave with whole lines: a store instruction
 // writes four rows' 128 bytes.  Without 16-byte alignment of the rows of C (``vec`` false) they leave one by one.
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
-// EPI 2: g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: as they are), g * sigmoid(alpha * g) * (u + 1).
-__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float alpha) {
-  if (limit > 0.f) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
+// The gated epilogue (EPI 1) in its general form: g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: as they
+// are), g * sigmoid(alpha * g) * (u + shift).  SiLU-and-multiply is {0, 1, 0}.
+struct GluParams { float limit = 0.f, alpha = 1.f, shift = 0.f; };
+__device__ __forceinline__ float gated(float g, float u, const GluParams& p) {
+  if (p.limit > 0.f) {
+    g = fminf(g, p.limit);
+    u = fminf(fmaxf(u, -p.limit), p.limit);
   }
-  return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+  return __fdividef(g, 1.0f + __expf(-p.alpha * g)) * (u + p.shift);
 }
 
 template <int EPI, typename TO, int OUT_COLS, typename Load, typename Fix>
 __device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char* stage, TO* __restrict__ C, int64_t ldc, int M, int N,
-                                           int m0, int n0, int lane_base, int lane, bool vec, float limit = 0.f, float alpha = 1.f) {
+                                           int m0, int n0, int lane_base, int lane, bool vec, GluParams glu = GluParams()) {
   const int m = m0 + lane_base + lane;
   // 32 results of the lane's row from output column ``c`` on
   auto results = [&](int c, float (&g)[32]) {
-    if (EPI == 1 || EPI == 2) {
+    if (EPI == 1) {
       float u[32];
       load(c, g);
       load(OUT_COLS + c, u);
@@ -75,7 +76,7 @@ __device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char
       fix(c, g);
       fix(OUT_COLS + c, u);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) g[j] = EPI == 1 ? silu_mul(g[j], u[j]) : clamped_glu(g[j], u[j], limit, alpha);
+      for (int j = 0; j < 32; ++j) g[j] = gated(g[j], u[j], glu);
     } else {
       load(c, g);
       tc5::wait_ld();
@@ -149,7 +150,7 @@ template <int BN, int EPI, typename TO, bool DEEP>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     TO* __restrict__ C, int64_t ldc, int M, int N, int K, int kb_per_split, int64_t split_stride,
-                    int* __restrict__ err) {
+                    int* __restrict__ err, GluParams glu) {
   constexpr int STAGES = tg_stages<BN>(DEEP);
   constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
@@ -235,7 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // every product is over and every load has been read: the ring's first 16 KB are the four warps' staging rows
       auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + col, v); };
       auto fix = [](int, float (&)[32]) {};
-      write_rows<EPI, TO, OUT_COLS>(load, fix, smem + (warp & 3) * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec);
+      write_rows<EPI, TO, OUT_COLS>(load, fix, smem + (warp & 3) * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec, glu);
     }
   }
   if (!ok) atomicOr(err + 1, 1);
@@ -247,7 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int BN, int EPI, typename TO, bool DEEP>
 int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int splits, int64_t split_stride,
-              int* err, cudaStream_t stream) {
+              int* err, cudaStream_t stream, GluParams glu = GluParams()) {
   constexpr int STAGES = tg_stages<BN>(DEEP);
   const size_t smem = (size_t)STAGES * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
   static bool attr_set = false;
@@ -260,24 +261,23 @@ int launch_tg(const void* map_a, const void* map_w, void* C, int64_t ldc, int M,
   const int num_kb = (K + TG_BK - 1) / TG_BK, kb_per_split = (num_kb + splits - 1) / splits;
   dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (M + TG_BM - 1) / TG_BM, (num_kb + kb_per_split - 1) / kb_per_split);
   me_launch(gemm_tcgen05_kernel<BN, EPI, TO, DEEP>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
-            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, kb_per_split, split_stride, err);
+            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, kb_per_split, split_stride, err, glu);
   return 0;
 }
 
 // ---- one product per expert (a routed feed-forward) ------------------------------------------------------------
 // The rows of A lie in expert order: expert e owns rows [offsets[e], offsets[e + 1]), numbers that exist on the device only.
-// W is [E][rows_w][K]; with EPI 2 an expert's rows are gate rows then up rows and the result is the clamped gated
-// activation.  The grid has a row tile to spare per expert; a block walks the offsets to find its expert and its rows and
+// W is [E][rows_w][K]; with EPI 1 an expert's rows are gate rows then up rows and the result is the gated activation.  The grid has a row tile to spare per expert; a block walks the offsets to find its expert and its rows and
 // leaves if there are none.  A tile's box of A may reach into the next expert's rows and its box of W into the next
 // expert's weights: those results are never stored.  Everything else is the kernel above.
 template <int BN, int EPI, typename TO>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                             TO* __restrict__ C, int64_t ldc, const int* __restrict__ offsets, int E, int N, int rows_w, int K,
-                            float limit, float alpha, int* __restrict__ err) {
+                            GluParams glu, int* __restrict__ err) {
   constexpr int STAGES = tg_stages<BN>(false);
   constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
-  constexpr int OUT_COLS = EPI == 2 ? BN / 2 : BN;
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
   extern __shared__ unsigned char tg_smem_raw[];
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
   __shared__ uint32_t tmem_slot;
@@ -320,7 +320,7 @@ gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         unsigned char* a_dst = smem + s * STAGE_BYTES;
         unsigned char* b_dst = a_dst + TG_A_BYTES;
         tma::mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        if (EPI == 2) {
+        if (EPI == 1) {
           tma::load_2d(b_dst, &map_w, kb * TG_BK, w0 + n0, &full_bar[s]);
           tma::load_2d(b_dst + B_BYTES / 2, &map_w, kb * TG_BK, w0 + N + n0, &full_bar[s]);
         } else {
@@ -353,7 +353,7 @@ gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (ok) {
       auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(tmem + ((uint32_t)lane_base << 16) + col, v); };
       auto fix = [](int, float (&)[32]) {};
-      write_rows<EPI, TO, OUT_COLS>(load, fix, smem + (warp & 3) * 4096, C, ldc, m_end, N, m0, n0, lane_base, lane, vec, limit, alpha);
+      write_rows<EPI, TO, OUT_COLS>(load, fix, smem + (warp & 3) * 4096, C, ldc, m_end, N, m0, n0, lane_base, lane, vec, glu);
     }
   }
   if (!ok) atomicOr(err + 1, 1);
@@ -365,7 +365,7 @@ gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
 template <int BN, int EPI, typename TO>
 int launch_grouped(const void* map_a, const void* map_w, void* C, int64_t ldc, const int* offsets, int E, int rows, int N, int rows_w,
-                   int K, float limit, float alpha, int* err, cudaStream_t stream) {
+                   int K, GluParams glu, int* err, cudaStream_t stream) {
   constexpr int STAGES = tg_stages<BN>(false);
   const size_t smem = (size_t)STAGES * (TG_A_BYTES + BN * TG_BK * 2) + 1024;
   static bool attr_set = false;
@@ -374,10 +374,10 @@ int launch_grouped(const void* map_a, const void* map_w, void* C, int64_t ldc, c
     ME_REQUIRE(e == cudaSuccess, "me_gemm_tcgen05_grouped: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  constexpr int OUT_COLS = EPI == 2 ? BN / 2 : BN;
+  constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
   dim3 grid((N + OUT_COLS - 1) / OUT_COLS, (rows + TG_BM - 1) / TG_BM + E);
   me_launch(gemm_tcgen05_grouped_kernel<BN, EPI, TO>, grid, dim3(TG_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(map_a),
-            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, offsets, E, N, rows_w, K, limit, alpha, err);
+            *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, offsets, E, N, rows_w, K, glu, err);
   return 0;
 }
 
@@ -392,7 +392,7 @@ template <int BN> constexpr int tp_stages() { return BN <= 128 ? 6 : 4; }
 template <int BN, int EPI, typename TO>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                               TO* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err) {
+                               TO* __restrict__ C, int64_t ldc, int M, int N, int K, int* __restrict__ err, GluParams glu) {
   constexpr int STAGES = tp_stages<BN>();
   constexpr int B_BYTES = BN * TG_BK * 2, STAGE_BYTES = TG_A_BYTES + B_BYTES;
   constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
@@ -516,7 +516,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
       if (ok) {
         auto load = [&](int col, float (&v)[32]) { tc5::ld_32cols(acc + col, v); };
         auto fix = [](int, float (&)[32]) {};
-        write_rows<EPI, TO, OUT_COLS>(load, fix, smem + STAGES * STAGE_BYTES + (warp & 3) * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec);
+        write_rows<EPI, TO, OUT_COLS>(load, fix, smem + STAGES * STAGE_BYTES + (warp & 3) * 4096, C, ldc, M, N, m0, n0, lane_base, lane, vec,
+                                      glu);
       }
       tc5::fence_before_sync();
       __syncwarp();
@@ -819,7 +820,8 @@ int launch_ts(const void* map_a, const void* map_w, void* C, int64_t ldc, int M,
 }
 
 template <int BN, int EPI, typename TO>
-int launch_tp(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream) {
+int launch_tp(const void* map_a, const void* map_w, void* C, int64_t ldc, int M, int N, int K, int* err, cudaStream_t stream,
+              GluParams glu = GluParams()) {
   const size_t smem = (size_t)tp_stages<BN>() * (TG_A_BYTES + BN * TG_BK * 2) + 4 * 4096 + 1024;      // the ring, the epilogue warps' staging rows
   static bool attr_set = false;
   if (!attr_set) {
@@ -832,7 +834,7 @@ int launch_tp(const void* map_a, const void* map_w, void* C, int64_t ldc, int M,
   ME_REQUIRE(tiles < (1ll << 30), "me_gemm_tcgen05: too many tiles");
   const int blocks = (int)(tiles < me_sm_count() ? tiles : me_sm_count());
   me_launch(gemm_tcgen05_persistent_kernel<BN, EPI, TO>, dim3(blocks), dim3(TG_THREADS), smem, stream,
-            *reinterpret_cast<const CUtensorMap*>(map_a), *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, err);
+            *reinterpret_cast<const CUtensorMap*>(map_a), *reinterpret_cast<const CUtensorMap*>(map_w), (TO*)C, ldc, M, N, K, err, glu);
   return 0;
 }
 
@@ -850,16 +852,19 @@ ME_API int me_gemm_tcgen05_w_box_rows(int bn, int epi) { return epi == 1 ? bn / 
 
 // The persistent form of me_gemm_tcgen05 (same operands, no split along K): bn 128 or 256.
 ME_API int me_gemm_tcgen05_persistent(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, int M, int N,
-                                      int K, int epi, int bn, int* err, cudaStream_t stream) {
+                                      int K, int epi, int bn, float glu_limit, float glu_alpha, float glu_shift, int* err,
+                                      cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   ME_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "me_gemm_tcgen05_persistent: bad sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
   ME_REQUIRE(map_a != nullptr && map_w != nullptr && err != nullptr, "me_gemm_tcgen05_persistent: tensor maps and the error word are required");
   ME_REQUIRE(epi == 0 || (epi == 1 && c_dtype == ME_BF16), "me_gemm_tcgen05_persistent: epilogue %d", epi);
   ME_REQUIRE(bn == 128 || bn == 256, "me_gemm_tcgen05_persistent: tile width %d is not 128 or 256", bn);
+  GluParams glu;
+  glu.limit = glu_limit, glu.alpha = glu_alpha, glu.shift = glu_shift;
   int rc = 1;
 #define ME_TP_CASE(BN_)                                                                                  \
   if (bn == BN_) {                                                                                       \
-    if (epi == 1) rc = launch_tp<BN_, 1, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream);              \
+    if (epi == 1) rc = launch_tp<BN_, 1, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream, glu);         \
     else if (c_dtype == ME_BF16) rc = launch_tp<BN_, 0, bf16>(map_a, map_w, C, ldc, M, N, K, err, stream); \
     else rc = launch_tp<BN_, 0, float>(map_a, map_w, C, ldc, M, N, K, err, stream);                      \
   }
@@ -898,11 +903,14 @@ ME_API int me_gemm_tcgen05_shared(const void* map_a, const void* map_w, void* C,
 }
 
 // map_a: X as [M][K], boxes 128 x 64, 128-byte swizzle; map_w: W as [rows][K], boxes
-// me_gemm_tcgen05_w_box_rows(bn, epi) x 64.  N counts output columns (epi 1: W has 2N rows).
+// me_gemm_tcgen05_w_box_rows(bn, epi) x 64.  N counts output columns (epi 1: W has 2N rows, gate rows then up rows, and the
+// result is g sigmoid(alpha g) (u + shift) with g and u clamped by ``glu_limit`` when that is positive; SiLU-and-multiply is
+// limit 0, alpha 1, shift 0).
 // bn is the accumulator's width: 64, 128 or 256.  ``splits`` > 1: the K range is shared out over that many blocks a tile, whose
 // float32 partial results lie ``split_stride`` elements apart (me_gemm_tcgen05_splits says how many there will be).
 ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, int M, int N,
-                           int K, int epi, int bn, int splits, int64_t split_stride, int* err, cudaStream_t stream) {
+                           int K, int epi, int bn, int splits, int64_t split_stride, float glu_limit, float glu_alpha, float glu_shift,
+                           int* err, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   ME_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0, "me_gemm_tcgen05: bad sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
   ME_REQUIRE(map_a != nullptr && map_w != nullptr && err != nullptr, "me_gemm_tcgen05: tensor maps and the error word are required");
@@ -912,11 +920,13 @@ ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_
              "me_gemm_tcgen05: %d splits (they need float32 results and no epilogue)", splits);
   ME_REQUIRE(bn == 64 || bn == 128 || bn == 256, "me_gemm_tcgen05: tile width %d is not 64, 128 or 256", bn);
   const int out_cols = epi == 1 ? bn / 2 : bn;
+  GluParams glu;
+  glu.limit = glu_limit, glu.alpha = glu_alpha, glu.shift = glu_shift;
   const bool deep = (int64_t)((N + out_cols - 1) / out_cols) * ((M + TG_BM - 1) / TG_BM) * me_gemm_tcgen05_splits(K, splits) <= me_sm_count();
   int rc = 1;
 #define ME_TG_CASE(BN_)                                                                                              \
   if (bn == BN_) {                                                                                                   \
-    if (epi == 1) rc = launch_tg<BN_, 1, bf16, false>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream);             \
+    if (epi == 1) rc = launch_tg<BN_, 1, bf16, false>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream, glu);        \
     else if (c_dtype == ME_BF16) rc = deep ? launch_tg<BN_, 0, bf16, true>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream)   \
                                            : launch_tg<BN_, 0, bf16, false>(map_a, map_w, C, ldc, M, N, K, 1, 0, err, stream); \
     else rc = deep ? launch_tg<BN_, 0, float, true>(map_a, map_w, C, ldc, M, N, K, splits, split_stride, err, stream)          \
@@ -941,9 +951,11 @@ ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C
              K, E, rows_w, N);
   ME_REQUIRE(!glu || c_dtype == ME_BF16, "me_gemm_tcgen05_grouped: the gated activation is written in bfloat16");
   int rc;
-  if (glu) rc = launch_grouped<128, 2, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, limit, alpha, err, stream);
-  else if (c_dtype == ME_F32) rc = launch_grouped<128, 0, float>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, limit, alpha, err, stream);
-  else rc = launch_grouped<128, 0, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, limit, alpha, err, stream);
+  GluParams gp;
+  gp.limit = limit, gp.alpha = alpha, gp.shift = 1.f;
+  if (glu) rc = launch_grouped<128, 1, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);
+  else if (c_dtype == ME_F32) rc = launch_grouped<128, 0, float>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);
+  else rc = launch_grouped<128, 0, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_gemm_tcgen05_grouped");
   return 0;

@@ -44,8 +44,8 @@ _PROTOS = {
                              _I, _I, _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _P],
     "me_gemm_stream": [_I, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
-    "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _P, _P],
-    "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P],
+    "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _F, _P, _P],
+    "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_shared": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _L, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
@@ -565,16 +565,23 @@ def tcgen05_one_round_width(M: int, N: int) -> int:
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: str, err: torch.Tensor,
                    tile_n: Optional[int] = None, splits: int = 1, persistent: Optional[bool] = None,
-                   share: Optional[bool] = None) -> None:
+                   share: Optional[bool] = None, glu: Optional[tuple[float, float, float]] = None) -> None:
     """The tcgen05 product of csrc/gemm_tcgen05.cu: TMA -> swizzled shared memory -> tcgen05.mma -> tensor memory.
+
+    ``glu`` = (limit, alpha, shift) with the "silu_mul" epilogue: the gated epilogue in its general form,
+    g sigmoid(alpha g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit) when limit > 0.
 
     With ``splits`` > 1 ``out`` is float32 [tcgen05_splits(K, splits), M, N]: partial results over parts of K.
     ``share``: the form that cuts the stages of all tiles into one equal range an SM (``tile_n`` 128 or 256)."""
     M, K = x.shape
     epi = {"none": 0, "silu_mul": 1}[epilogue]
+    _need(glu is None or epi == 1, "linear_tcgen05: the gate's parameters go with the gated epilogue")
+    glu_params = tuple(float(v) for v in (glu or (0.0, 1.0, 0.0)))
     N = weight.shape[0] // 2 if epi else weight.shape[0]
     if share is None and tile_n is None and persistent is None and splits == 1 and tcgen05_share == "auto" and tcgen05_takes(x, weight):
         share = tcgen05_share_pays(M, N, K, epi)
+    if share and glu is not None:
+        share = False                 # (the work-sharing form has no gated epilogue)
     if share:
         bn = tile_n or 256
         _need(tcgen05_takes(x, weight) and splits == 1 and bn in (128, 256), "linear_tcgen05: operands not taken by the work-sharing form")
@@ -617,10 +624,10 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epi
         persistent = False
     if persistent and splits == 1 and bn >= 128:
         _call("me_gemm_tcgen05_persistent", matrix_tensor_map(x, 128).ptr, matrix_tensor_map(weight, box_w).ptr, out.data_ptr(),
-              _dt(out), ldc, M, N, K, epi, bn, err.data_ptr(), _stream())
+              _dt(out), ldc, M, N, K, epi, bn, *glu_params, err.data_ptr(), _stream())
         return
     _call("me_gemm_tcgen05", matrix_tensor_map(x, 128).ptr, matrix_tensor_map(weight, box_w).ptr, out.data_ptr(), _dt(out),
-          ldc, M, N, K, epi, bn, splits, split_stride, err.data_ptr(), _stream())
+          ldc, M, N, K, epi, bn, splits, split_stride, *glu_params, err.data_ptr(), _stream())
 
 
 def tcgen05_splits(K: int, splits: int) -> int:

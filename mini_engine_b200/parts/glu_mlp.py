@@ -39,9 +39,16 @@ class ClampedGLU(FeedForward):
         return self.gate_up.weight
 
     def forward(self, x, ctx, out_name: str = "ffn_out", out_dtype=None):
-        z = self.gate_up.forward(x, ctx, out_name + "_gate_up")
-        act = ctx.buffer(out_name + "_act", (z.shape[0], self.intermediate_size), ctx.act_dtype)
-        ops.clamped_glu(z, act, self.limit, self.alpha)
+        act = ctx.buffer(out_name + "_act", (x.shape[0], self.intermediate_size), ctx.act_dtype)
+        w = self.gate_up.weight
+        if (ctx.act_dtype == torch.bfloat16 and ops.use_tcgen05_gemm and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and ops.tcgen05_takes(x, w)):
+            # a long step: the activation is the epilogue of the tcgen05 product, as SiLU is in a SwiGLU
+            ops.tag = out_name + "_act"
+            ops.linear_tcgen05(x, w, act, "silu_mul", ctx.error_flag, glu=(self.limit, self.alpha, 1.0))
+        else:
+            z = self.gate_up.forward(x, ctx, out_name + "_gate_up")
+            ops.clamped_glu(z, act, self.limit, self.alpha)
         return self.down.forward(act, ctx, out_name, out_dtype=out_dtype)
 
 

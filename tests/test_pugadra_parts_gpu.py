@@ -277,6 +277,26 @@ def test_clamped_gated_activation(dtype, limit):
     assert torch.allclose(out.float().cpu().double(), ref, atol=ATOL[dtype], rtol=1e-2 if dtype == "bfloat16" else 1e-5)
 
 
+@pytest.mark.parametrize("limit", [None, 0.9])
+@pytest.mark.parametrize("T, W, F", [(256, 128, 192), (2048, 256, 1024), (300, 72, 200)])
+def test_clamped_gated_activation_as_the_epilogue_of_the_tcgen05_product(limit, T, W, F):
+    """A long step's gate|up product with the activation in its epilogue (the one-tile and the persistent form) against the
+    plain function."""
+    ops = _ops()
+    h = torch.randn(T, W, generator=g(1)).bfloat16()
+    w = {"gate": (torch.randn(F, W, generator=g(2)) * 0.2).bfloat16(), "up": (torch.randn(F, W, generator=g(3)) * 0.2).bfloat16()}
+    gate, up = h.double() @ w["gate"].double().T, h.double() @ w["up"].double().T
+    if limit is not None:
+        gate, up = gate.clamp(max=limit), up.clamp(-limit, limit)
+    ref = gate * torch.sigmoid(1.702 * gate) * (up + 1)
+    err = torch.zeros(4, dtype=torch.int32, device=DEV)
+    out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+    packed = torch.cat((w["gate"], w["up"])).to(DEV).contiguous()
+    ops.linear_tcgen05(h.to(DEV), packed, out, "silu_mul", err, glu=(limit or 0.0, 1.702, 1.0))
+    assert not err.any()
+    assert torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T, E, top, W, F", [(37, 6, 2, 64, 40), (5, 5, 3, 52, 22), (130, 16, 2, 128, 64), (64, 3, 3, 40, 24),
                                              (1, 4, 1, 64, 32), (300, 12, 1, 96, 160), (700, 8, 2, 192, 320), (1100, 5, 1, 72, 200)])
