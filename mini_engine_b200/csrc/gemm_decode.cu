@@ -37,7 +37,8 @@ __global__ void __launch_bounds__(DL_MAX_WARPS * 32)
 gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restrict__ sumsq_in, int sumsq_parts, float eps,
                    const bf16* __restrict__ W, TO* __restrict__ Y, int64_t ldy, float* __restrict__ res_out,
                    float* __restrict__ sumsq_out, const float* __restrict__ next_w, bf16* __restrict__ xw_out, int M,
-                   int N, int K, const unsigned char* __restrict__ ahead, unsigned long long ahead_bytes) {
+                   int N, int K, const unsigned char* __restrict__ ahead, unsigned long long ahead_bytes, float glu_limit,
+                   float glu_alpha, float glu_shift) {
   extern __shared__ __align__(128) unsigned char dl_smem[];
   // The weights of the product that runs after this one are asked into L2 now: a decode step is a chain of
   // short dependent kernels, and without this the memory system idles while each waits for the one before.
@@ -173,8 +174,12 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
       const int m = idx >> 3, r = idx & 7;
       const int n = strip * 8 + r;
       if (m >= M || n >= N) continue;
-      const float gate = total(r, m) * row_scale[m], up = total(r + 8, m) * row_scale[m];
-      Y[(int64_t)m * ldy + n] = from_f<TO>(gate / (1.0f + expf(-gate)) * up);
+      float gate = total(r, m) * row_scale[m], up = total(r + 8, m) * row_scale[m];
+      if (glu_limit > 0.f) {                        // the gated epilogue in its general form (SiLU-and-multiply: 0, 1, 0)
+        gate = fminf(gate, glu_limit);
+        up = fminf(fmaxf(up, -glu_limit), glu_limit);
+      }
+      Y[(int64_t)m * ldy + n] = from_f<TO>(gate / (1.0f + expf(-glu_alpha * gate)) * (up + glu_shift));
     }
   } else if (EPI == 2) {
     // R consecutive threads hold the R columns of one row: add into the residual, then the row's sum of squares
@@ -208,7 +213,8 @@ gemm_decode_kernel(const bf16* __restrict__ X, int64_t ldx, const float* __restr
 template <int EPI, typename TO, int R>
 int launch_dl(int strips, int warps, cudaStream_t stream, const void* X, int64_t ldx, const float* sumsq_in, int sumsq_parts,
               float eps, const void* W, void* Y, int64_t ldy, float* res_out, float* sumsq_out, const float* next_w,
-              void* xw_out, int M, int N, int K, const void* ahead, unsigned long long ahead_bytes) {
+              void* xw_out, int M, int N, int K, const void* ahead, unsigned long long ahead_bytes, float glu_limit, float glu_alpha,
+              float glu_shift) {
   const size_t smem = (size_t)warps * (2 * 16 * DL_KW * sizeof(bf16) + 16 * 17 * sizeof(float));
   static size_t attr = 0;
   if (smem > attr) {
@@ -218,7 +224,7 @@ int launch_dl(int strips, int warps, cudaStream_t stream, const void* X, int64_t
   }
   me_launch(gemm_decode_kernel<EPI, TO, R>, dim3(strips), dim3(warps * 32), smem, stream, (const bf16*)X, ldx, sumsq_in,
             sumsq_parts, eps, (const bf16*)W, (TO*)Y, ldy, res_out, sumsq_out, next_w, (bf16*)xw_out, M, N, K,
-            (const unsigned char*)ahead, ahead_bytes);
+            (const unsigned char*)ahead, ahead_bytes, glu_limit, glu_alpha, glu_shift);
   return 0;
 }
 }  // namespace
@@ -233,7 +239,8 @@ ME_API int me_gemm_decode_sumsq_parts(int N) { const int r = strip_rows(N); retu
 
 // X bfloat16 [M][ldx].  sumsq_in (or null) [sumsq_parts][M] with eps: the results of row m are multiplied by
 // rsqrt(sum_p sumsq_in[p][m] / K + eps).
-// epi 0: Y (y_dtype) [M][ldy]; epi 1: SiLU-and-multiply (weight rows gate | up, N = columns of Y);
+// epi 0: Y (y_dtype) [M][ldy]; epi 1: the gated epilogue g sigmoid(alpha g) (u + shift), g and u clamped by glu_limit when that
+// is positive (weight rows gate | up, N = columns of Y; SiLU-and-multiply is limit 0, alpha 1, shift 0);
 // epi 2: res_out [M][N] += X W^T, sumsq_out [me_gemm_decode_sumsq_parts(N)][M] and, with next_w [N], xw_out
 // bfloat16 [M][N] = res_out * next_w.
 // ahead (or null), ahead_bytes: memory that a later kernel will read (the next product's weights), asked into
@@ -241,7 +248,7 @@ ME_API int me_gemm_decode_sumsq_parts(int N) { const int r = strip_rows(N); retu
 ME_API int me_gemm_decode(int epi, const void* X, int64_t ldx, const float* sumsq_in, int sumsq_parts, float eps,
                           const void* W, void* Y, int y_dtype, int64_t ldy, float* res_out, float* sumsq_out,
                           const float* next_w, void* xw_out, int M, int N, int K, const void* ahead,
-                          unsigned long long ahead_bytes, cudaStream_t stream) {
+                          unsigned long long ahead_bytes, float glu_limit, float glu_alpha, float glu_shift, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   ME_REQUIRE(M > 0 && M <= 16, "me_gemm_decode: M=%d is not in 1..16", M);
   ME_REQUIRE(K % 8 == 0 && K > 0 && K <= DL_MAX_WARPS * DL_KW, "me_gemm_decode: K=%d must be a multiple of 8 up to %d", K,
@@ -259,7 +266,7 @@ ME_API int me_gemm_decode(int epi, const void* X, int64_t ldx, const float* sums
   int rc = 1;
 #define ME_DL(EPI_, TO_, R_)                                                                                        \
   rc = launch_dl<EPI_, TO_, R_>(strips, warps, stream, X, ldx, sumsq_in, sumsq_parts, eps, W, Y, ldy, res_out, sumsq_out, \
-                                next_w, xw_out, M, N, K, ahead, ahead_bytes)
+                                next_w, xw_out, M, N, K, ahead, ahead_bytes, glu_limit, glu_alpha, glu_shift)
   if (epi == 2) {
     if (rows == 8) ME_DL(2, float, 8); else ME_DL(2, float, 16);
   } else if (epi == 1) {

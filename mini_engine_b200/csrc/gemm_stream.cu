@@ -57,7 +57,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                    const float* __restrict__ sumsq_in, int sumsq_parts, float eps, TO* __restrict__ Y, int64_t ldy,
                    float* __restrict__ res_out, float* __restrict__ sumsq_out, const float* __restrict__ next_w,
                    bf16* __restrict__ xw_out, int M, int N, int K, int groups, float* __restrict__ partials,
-                   int* __restrict__ flags, int* __restrict__ err) {
+                   int* __restrict__ flags, int* __restrict__ err, float glu_limit, float glu_alpha, float glu_shift) {
   constexpr int STAGES = gs_stages<XR>(), STAGE_BYTES = gs_stage_bytes<XR>();
   constexpr int COLS = EPI == 1 ? GS_ROWS / 2 : GS_ROWS;         // output columns of a group
   extern __shared__ unsigned char gs_smem_raw[];
@@ -250,8 +250,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           const int idx = tid + i * GS_CONSUMERS, m = idx / COLS, r = idx % COLS;
           const int n = grp * COLS + r;
           if (m < M && n < N) {
-            const float gate = red[r][m], up = red[COLS + r][m];
-            Y[(int64_t)m * ldy + n] = from_f<TO>(gate / (1.0f + expf(-gate)) * up);
+            float gate = red[r][m], up = red[COLS + r][m];
+            if (glu_limit > 0.f) {                  // the gated epilogue in its general form (SiLU-and-multiply: 0, 1, 0)
+              gate = fminf(gate, glu_limit);
+              up = fminf(fmaxf(up, -glu_limit), glu_limit);
+            }
+            Y[(int64_t)m * ldy + n] = from_f<TO>(gate / (1.0f + expf(-glu_alpha * gate)) * (up + glu_shift));
           }
         }
       } else {
@@ -295,7 +299,7 @@ int gs_blocks(int groups, int n_its) {
 template <int EPI, typename TO, int XR>
 int launch_gs(cudaStream_t stream, const void* map_w, const void* map_x, const float* sumsq_in, int sumsq_parts, float eps, void* Y,
               int64_t ldy, float* res_out, float* sumsq_out, const float* next_w, void* xw_out, int M, int N, int K,
-              float* partials, int* flags, int* err) {
+              float* partials, int* flags, int* err, float glu_limit, float glu_alpha, float glu_shift) {
   const size_t smem = (size_t)gs_stages<XR>() * gs_stage_bytes<XR>() + 1024;
   static bool attr_set = false;
   if (!attr_set) {
@@ -306,7 +310,8 @@ int launch_gs(cudaStream_t stream, const void* map_w, const void* map_x, const f
   const int groups = EPI == 1 ? (2 * N + GS_ROWS - 1) / GS_ROWS : (N + GS_ROWS - 1) / GS_ROWS, n_its = (K + GS_BK - 1) / GS_BK;
   me_launch(gemm_stream_kernel<EPI, TO, XR>, dim3(gs_blocks(groups, n_its)), dim3(GS_THREADS), smem, stream,
             *reinterpret_cast<const CUtensorMap*>(map_w), *reinterpret_cast<const CUtensorMap*>(map_x), sumsq_in, sumsq_parts, eps,
-            (TO*)Y, ldy, res_out, sumsq_out, next_w, (bf16*)xw_out, M, N, K, groups, partials, flags, err);
+            (TO*)Y, ldy, res_out, sumsq_out, next_w, (bf16*)xw_out, M, N, K, groups, partials, flags, err, glu_limit, glu_alpha,
+            glu_shift);
   return 0;
 }
 }  // namespace
@@ -329,7 +334,8 @@ ME_API int me_gemm_stream_flag_ints() { return me_sm_count(); }
 // that share them must not overlap on the device).  err: int32[4]; flag 1 is set when a wait ran out.
 ME_API int me_gemm_stream(int epi, const void* map_x, const float* sumsq_in, int sumsq_parts, float eps, const void* map_w,
                           void* Y, int y_dtype, int64_t ldy, float* res_out, float* sumsq_out, const float* next_w,
-                          void* xw_out, int M, int N, int K, float* partials, int* flags, int* err, cudaStream_t stream) {
+                          void* xw_out, int M, int N, int K, float* partials, int* flags, int* err, float glu_limit, float glu_alpha,
+                          float glu_shift, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   ME_REQUIRE(M > 0 && M <= 16, "me_gemm_stream: M=%d is not in 1..16", M);
   ME_REQUIRE(K % 8 == 0 && K > 0, "me_gemm_stream: K=%d must be a positive multiple of 8", K);
@@ -342,9 +348,9 @@ ME_API int me_gemm_stream(int epi, const void* map_x, const float* sumsq_in, int
   int rc = 1;
 #define ME_GS(EPI_, TO_)                                                                                                      \
   rc = M <= 8 ? launch_gs<EPI_, TO_, 8>(stream, map_w, map_x, sumsq_in, sumsq_parts, eps, Y, ldy, res_out, sumsq_out, next_w,  \
-                                        xw_out, M, N, K, partials, flags, err)                                                 \
+                                        xw_out, M, N, K, partials, flags, err, glu_limit, glu_alpha, glu_shift)                \
               : launch_gs<EPI_, TO_, 16>(stream, map_w, map_x, sumsq_in, sumsq_parts, eps, Y, ldy, res_out, sumsq_out, next_w, \
-                                         xw_out, M, N, K, partials, flags, err)
+                                         xw_out, M, N, K, partials, flags, err, glu_limit, glu_alpha, glu_shift)
   if (epi == 2) {
     ME_GS(2, float);
   } else if (epi == 1) {

@@ -42,8 +42,8 @@ _PROTOS = {
     "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _I, _P, _L, _P],
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _I, _I, _P, _P],
-    "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _P],
-    "me_gemm_stream": [_I, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
+    "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _F, _F, _F, _P],
+    "me_gemm_stream": [_I, _P, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _F, _F, _F, _P],
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_shared": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
@@ -426,7 +426,7 @@ def decode_linear_sumsq_parts(N: int, K: int = 0, stream: Optional[bool] = None)
 def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.Tensor] = None, epilogue: str = "none",
                   row_scale=None, residual_out: Optional[torch.Tensor] = None, sumsq_out: Optional[torch.Tensor] = None,
                   next_norm=None, fetch_ahead: Optional[torch.Tensor] = None, err: Optional[torch.Tensor] = None,
-                  kernel: Optional[str] = None) -> None:
+                  kernel: Optional[str] = None, glu: Optional[tuple[float, float, float]] = None) -> None:
     """One decode product with its neighbours folded in (csrc/gemm_decode.cu, csrc/gemm_stream.cu; ``kernel``:
     "stream" asks for the latter whatever ``decode_kernel`` says).
 
@@ -436,8 +436,11 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
     "residual": residual_out += x W^T; ``sumsq_out`` [decode_linear_sumsq_parts(N), M] gets the new residual's sums
     of squares per strip of columns, and with ``next_norm`` = (weight float32 [N], xw bfloat16 [M, N]) xw gets the new
     residual times that weight).  ``fetch_ahead``: a tensor that a later kernel reads (the next product's weight);
-    this kernel asks it into L2."""
+    this kernel asks it into L2.  ``glu`` = (limit, alpha, shift) with "silu_mul": the gated epilogue in its general form,
+    g sigmoid(alpha g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit) when limit > 0."""
     epi = {"none": 0, "silu_mul": 1, "residual": 2}[epilogue]
+    _need(glu is None or epi == 1, "decode_linear: the gate's parameters go with the gated epilogue")
+    glu_params = tuple(float(v) for v in (glu or (0.0, 1.0, 0.0)))
     M, K = x.shape
     _need(x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "decode_linear: x")
     stream = kernel == "stream" or _decode_uses_stream(K)
@@ -468,11 +471,12 @@ def decode_linear(weight: torch.Tensor, x: torch.Tensor, *, out: Optional[torch.
         _call("me_gemm_stream", epi, matrix_tensor_map(x, lib.me_gemm_stream_x_box_rows(M)).ptr, _ptr(sumsq),
               sumsq.shape[0] if sumsq is not None else 0, float(eps), matrix_tensor_map(weight, lib.me_gemm_stream_w_box_rows(epi)).ptr, yp, ydt, ldy,
               _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K, partials.data_ptr(), flags.data_ptr(),
-              err.data_ptr(), _stream())
+              err.data_ptr(), *glu_params, _stream())
         return
     _call("me_gemm_decode", epi, x.data_ptr(), x.stride(0), _ptr(sumsq), sumsq.shape[0] if sumsq is not None else 0, float(eps),
           weight.data_ptr(), yp, ydt, ldy, _ptr(residual_out), _ptr(sumsq_out), _ptr(nw), _ptr(xw), M, N, K,
-          _ptr(fetch_ahead), fetch_ahead.numel() * fetch_ahead.element_size() if fetch_ahead is not None else 0, _stream())
+          _ptr(fetch_ahead), fetch_ahead.numel() * fetch_ahead.element_size() if fetch_ahead is not None else 0, *glu_params,
+          _stream())
 
 
 TCGEN05_MIN_ROWS = 128    # rows from which bfloat16 products run csrc/gemm_tcgen05.cu whatever the weight (fewer: cuBLAS) ...

@@ -46,6 +46,12 @@ class ClampedGLU(FeedForward):
             # a long step: the activation is the epilogue of the tcgen05 product, as SiLU is in a SwiGLU
             ops.tag = out_name + "_act"
             ops.linear_tcgen05(x, w, act, "silu_mul", ctx.error_flag, glu=(self.limit, self.alpha, 1.0))
+        elif (ctx.act_dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+              and ops.decode_linear_takes(x.shape[0], self.hidden_size, w, False)):
+            # a step of up to 16 tokens: the same in the epilogue of the decode products
+            ops.tag = out_name + "_act"
+            ops.decode_linear(w, x, out=act, epilogue="silu_mul", fetch_ahead=self.down.weight, err=ctx.error_flag,
+                              glu=(self.limit, self.alpha, 1.0))
         else:
             z = self.gate_up.forward(x, ctx, out_name + "_gate_up")
             ops.clamped_glu(z, act, self.limit, self.alpha)

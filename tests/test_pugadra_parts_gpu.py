@@ -278,10 +278,11 @@ def test_clamped_gated_activation(dtype, limit):
 
 
 @pytest.mark.parametrize("limit", [None, 0.9])
-@pytest.mark.parametrize("T, W, F", [(256, 128, 192), (2048, 256, 1024), (300, 72, 200)])
-def test_clamped_gated_activation_as_the_epilogue_of_the_tcgen05_product(limit, T, W, F):
-    """A long step's gate|up product with the activation in its epilogue (the one-tile and the persistent form) against the
-    plain function."""
+@pytest.mark.parametrize("T, W, F", [(256, 128, 192), (2048, 256, 1024), (300, 72, 200), (8, 128, 192), (5, 4096, 264), (16, 1024, 520)])
+def test_clamped_gated_activation_as_the_epilogue_of_the_products(limit, T, W, F):
+    """The gate|up product with the activation in its epilogue against the plain function: a long step (the one-tile and the
+    persistent form of the tcgen05 product) and a step of up to 16 tokens (the decode product, and its streaming form from
+    K 3,072 on)."""
     ops = _ops()
     h = torch.randn(T, W, generator=g(1)).bfloat16()
     w = {"gate": (torch.randn(F, W, generator=g(2)) * 0.2).bfloat16(), "up": (torch.randn(F, W, generator=g(3)) * 0.2).bfloat16()}
@@ -292,7 +293,11 @@ def test_clamped_gated_activation_as_the_epilogue_of_the_tcgen05_product(limit, 
     err = torch.zeros(4, dtype=torch.int32, device=DEV)
     out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
     packed = torch.cat((w["gate"], w["up"])).to(DEV).contiguous()
-    ops.linear_tcgen05(h.to(DEV), packed, out, "silu_mul", err, glu=(limit or 0.0, 1.702, 1.0))
+    if T > 16:
+        ops.linear_tcgen05(h.to(DEV), packed, out, "silu_mul", err, glu=(limit or 0.0, 1.702, 1.0))
+    else:
+        assert ops.decode_linear_takes(T, W, packed, False)
+        ops.decode_linear(packed, h.to(DEV), out=out, epilogue="silu_mul", err=err, glu=(limit or 0.0, 1.702, 1.0))
     assert not err.any()
     assert torch.allclose(out.float().cpu().double(), ref, atol=2e-2, rtol=2e-2)
 
