@@ -116,6 +116,7 @@ class DecoderModel(Part):
     def forward(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         """Hidden states of the wanted rows, normalised: ``[len(ctx.logits_rows), hidden]``."""
         ctx.token_ids = token_ids
+        ctx.forward_serial = getattr(ctx, "forward_serial", 0) + 1      # what parts cache for ONE pass over the layers is keyed by this
         residual = self.embed.forward(token_ids, ctx)
         delta = None
         for i, call in enumerate(self.schedule):

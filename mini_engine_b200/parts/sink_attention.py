@@ -99,8 +99,12 @@ class SinkAttention(Mixer):
         inv_freq = self.rope.inv_freq if self.rope is not None else self._no_freq
         angles = None
         if self.rope is not None and T >= ops.ROPE_TABLE_MIN_TOKENS:
-            # one table a step for all layers that share the rotation (the step's metadata object lives as long as the step)
-            tables = ctx.attn_meta.__dict__.setdefault("rope_tables", {})
+            # One table for all layers that share the rotation, made anew in every pass over the layers (a pass that is being
+            # recorded into a graph must launch it too, or the replay would rotate by the positions of the recording).
+            cache = getattr(ctx, "_rope_tables", None)
+            if cache is None or cache[0] != ctx.forward_serial:
+                cache = ctx._rope_tables = (ctx.forward_serial, {})
+            tables = cache[1]
             angles = tables.get(id(self.rope))
             if angles is None:
                 angles = tables[id(self.rope)] = ctx.buffer(f"rope_table_{self.rope.rotary_dim}_{self.rope.theta!r}",

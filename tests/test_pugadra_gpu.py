@@ -148,6 +148,21 @@ def test_a_far_key_decides_the_logits():
         assert _error(got[f"{tag}0"], ref).max() < 5e-5, tag
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_of_one_size_replayed_from_a_graph(dtype):
+    """Four portions of 130 tokens with one wanted place each: the shape comes again, so the engine records the step and
+    replays it, at other positions each time (a rotation taken from the recording's positions would show at once)."""
+    name = "C"
+    r = helpers.random_requests(zoo.ALL[name][0]["vocab"], (520,), seed=41)[0]
+    steps = [{"step": k, "entries": [{"id": "g0", "tokens": r[130 * k:130 * (k + 1)], "want": [129]}], "end": ["g0"] if k == 3 else []}
+             for k in range(4)]
+    got, rp = _replay(name, dtype, steps)
+    assert rp.runner._prefill_graphs, "the step was never replayed from a graph"
+    ref = _plain_logits(name, r)[[129, 259, 389, 519]]
+    err = _error(got["g0"], ref)
+    assert err.max() < (TOL[dtype] if dtype == "float32" else 0.15), err
+
+
 def _plain_greedy(name, prompt, n):
     cfg, w = plain_pugadra.load_folder(zoo.folder(name))
     ids = list(prompt)
