@@ -940,10 +940,10 @@ ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_
 }
 
 // One product per expert over rows in expert order (see gemm_tcgen05_grouped_kernel).  map_a: A [rows, K], boxes 128 x 64;
-// map_w: W as [E * rows_w, K], boxes 128 x 64 (glu: 64 x 64, and rows_w = 2 N: gate rows then up rows).  C [rows, N]:
+// map_w: W as [E * rows_w, K], boxes bn x 64 (glu: bn / 2 x 64, and rows_w = 2 N: gate rows then up rows); bn: 128 or 256.  C [rows, N]:
 // bfloat16 with ``glu`` (the clamped gated activation), float32 or bfloat16 without.  ``rows`` bounds the grid.
 ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, const int* offsets, int E,
-                                   int rows, int N, int rows_w, int K, int glu, float limit, float alpha, int* err,
+                                   int rows, int N, int rows_w, int K, int glu, float limit, float alpha, int bn, int* err,
                                    cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   ME_REQUIRE(map_a && map_w && err && offsets, "me_gemm_tcgen05_grouped: missing operand");
@@ -953,9 +953,13 @@ ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C
   int rc;
   GluParams gp;
   gp.limit = limit, gp.alpha = alpha, gp.shift = 1.f;
-  if (glu) rc = launch_grouped<128, 1, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);
-  else if (c_dtype == ME_F32) rc = launch_grouped<128, 0, float>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);
-  else rc = launch_grouped<128, 0, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);
+  ME_REQUIRE(bn == 128 || bn == 256, "me_gemm_tcgen05_grouped: tile width %d is not 128 or 256", bn);
+#define ME_GROUPED(BN_)                                                                                                          \
+  if (glu) rc = launch_grouped<BN_, 1, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);             \
+  else if (c_dtype == ME_F32) rc = launch_grouped<BN_, 0, float>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream); \
+  else rc = launch_grouped<BN_, 0, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream)
+  if (bn == 256) { ME_GROUPED(256); } else { ME_GROUPED(128); }
+#undef ME_GROUPED
   if (rc) return rc;
   ME_LAUNCH_CHECK("me_gemm_tcgen05_grouped");
   return 0;

@@ -62,7 +62,7 @@ _PROTOS = {
     "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
     "me_moe_gather": [_P, _I, _L, _P, _I, _P, _I, _I, _P],
-    "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _P, _P],
+    "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
     "me_moe_combine": [_P, _L, _P, _P, _I, _P, _I, _L, _P, _I, _L, _I, _I, _P],
     "me_token_side_gate": [_P, _I, _L, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _P],
 }
@@ -1346,6 +1346,7 @@ def moe_route_sort(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int,
 
 
 use_moe_mma = True        # bfloat16 expert products on the tensor cores where the sizes allow; a switch for comparisons
+moe_tcgen05_tile_n = 0    # 0: by rule; 128 or 256: the accumulator's width of the experts' tcgen05 product (for comparisons)
 MOE_TCGEN05_MIN_ROWS = 512   # (token, choice) pairs from which the experts' products run the tcgen05 kernel (tiles of 128 rows)
 
 
@@ -1372,9 +1373,10 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
             _call("me_moe_gather", a.data_ptr(), _dt(a), a.stride(0), order.data_ptr(), top, gathered.data_ptr(), rows, K, _stream())
             a = gathered
         if a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0:
-            _call("me_gemm_tcgen05_grouped", matrix_tensor_map(a, 128).ptr, matrix_tensor_map(weight.view(E * NN, K), 64 if glu else 128).ptr,
+            bn = moe_tcgen05_tile_n if moe_tcgen05_tile_n else (256 if N >= 256 else 128)
+            _call("me_gemm_tcgen05_grouped", matrix_tensor_map(a, 128).ptr, matrix_tensor_map(weight.view(E * NN, K), bn // 2 if glu else bn).ptr,
                   out.data_ptr(), _dt(out), out.stride(0), offsets.data_ptr(), E, rows, N, NN, K, 1 if glu else 0, float(limit),
-                  float(alpha), err.data_ptr(), _stream())
+                  float(alpha), bn, err.data_ptr(), _stream())
             return
         order = None
     _call("me_moe_gemm", a.data_ptr(), _dt(a), a.stride(0), _ptr(order), top, weight.data_ptr(), _dt(weight), weight.stride(0),
