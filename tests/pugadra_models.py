@@ -67,7 +67,7 @@ C = config(130, 128, [
     attn(8, 2, 64, 64, conv=3, rot=64, mask=96, mlp=dense(256, 2.0)),
     attn(8, 2, 64, 64, conv=3, rot=64, mask=128, kv_from=0, mlp=moe(16, 2, 64, 2.0, shared=(64, 2.0))),
     attn(4, 4, 32, 64, conv=2, rot=16, base=1e6, mlp=moe(8, 4, 48, 1.0)),
-], eps=1e-5, mult=0.3, side=16)
+], eps=1e-5, mult=0.35, side=16)
 # D: no convolution, as many kv heads as heads, a window of ONE token (a query sees itself and the sink), every expert chosen
 D = config(64, 40, [
     attn(2, 2, 8, 8, rot=8, base=50.0, mask=1, mlp=moe(3, 3, 24, 2.0)),

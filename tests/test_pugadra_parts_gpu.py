@@ -41,7 +41,7 @@ def g(seed):
 
 
 # ---- the norm on both sides of a sub-layer -------------------------------------------------------------------
-@pytest.mark.parametrize("W", [40, 192, 1030, 4100])
+@pytest.mark.parametrize("W", [40, 200, 1030, 4100])
 def test_scaled_normed_update_and_the_next_norm(W):
     ops = _ops()
     T, eps, mult = 6, 1e-5, 0.3
@@ -207,7 +207,7 @@ ATOL = {"float32": 2e-5, "bfloat16": 2e-2}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H, G, D, V, window, ps", [(4, 2, 16, 24, 40, 16), (3, 1, 10, 9, 33, 8), (6, 1, 48, 48, 96, 16),
+@pytest.mark.parametrize("H, G, D, V, window, ps", [(4, 2, 16, 24, 40, 16), (3, 1, 10, 9, 33, 8), (10, 2, 40, 40, 72, 16),
                                                     (8, 2, 64, 64, 128, 16), (4, 4, 32, 64, None, 32), (2, 2, 8, 8, 1, 16),
                                                     (8, 1, 128, 128, 200, 64), (5, 5, 6, 5, 7, 8)])
 def test_attention_in_prompts_and_single_tokens(dtype, H, G, D, V, window, ps):
@@ -227,7 +227,7 @@ def test_attention_without_sink_and_without_gate(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window, ps, D", [(40, 16, 16), (33, 8, 10), (96, 16, 48), (128, 16, 64), (64, 64, 64)])
+@pytest.mark.parametrize("window, ps, D", [(40, 16, 16), (33, 8, 10), (72, 16, 40), (128, 16, 64), (64, 64, 64)])
 @pytest.mark.parametrize("delta", [0, 1])
 def test_a_key_at_the_windows_edge(dtype, window, ps, D, delta):
     """One key gets a score far above the others: the last one inside the window (delta 0: nearly all the weight must go
@@ -304,7 +304,7 @@ def test_clamped_gated_activation_as_the_epilogue_of_the_products(limit, T, W, F
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T, E, top, W, F", [(37, 6, 2, 64, 40), (5, 5, 3, 52, 22), (130, 16, 2, 128, 64), (64, 3, 3, 40, 24),
-                                             (1, 4, 1, 64, 32), (300, 12, 1, 96, 160), (700, 8, 2, 192, 320), (1100, 5, 1, 72, 200)])
+                                             (1, 4, 1, 64, 32), (300, 11, 1, 96, 160), (700, 8, 2, 200, 320), (1100, 5, 1, 72, 200)])
 def test_routed_experts_against_the_plain_loop(dtype, T, E, top, W, F):
     """Routing, grouping by expert, both products and the weighted sum, with and without a shared expert's output."""
     ops = _ops()
