@@ -79,7 +79,7 @@ def test_the_update_is_normalised_before_it_is_added():
 
 # ---- bias, convolution with state, rotation, cache write -----------------------------------------------------
 @pytest.mark.parametrize("taps, H, G, D, V, rot, own_kv", [(3, 4, 2, 16, 24, 8, True), (1, 3, 1, 10, 9, 6, True), (4, 6, 3, 6, 5, 0, True),
-                                                          (2, 5, 5, 8, 8, 8, False), (0, 2, 1, 12, 7, 12, True)])
+                                                          (2, 5, 5, 8, 8, 8, False), (0, 2, 1, 12, 7, 12, True), (6, 2, 2, 8, 6, 4, True)])
 @pytest.mark.parametrize("table", [False, True])
 def test_projections_through_convolution_and_rotation_in_portions_with_slots_used_again(taps, H, G, D, V, rot, own_kv, table):
     """``table``: the cosines and sines come from the step's table instead of being formed by every thread."""
